@@ -1,0 +1,171 @@
+"""TOML -> pydantic configuration tree.
+
+The key names, defaults and validators follow the reference schema
+(src/config.py:19-153) so every reference TOML loads unchanged; unknown keys are
+rejected everywhere.  Two optional tables are additions of this framework:
+``[checkpoint]`` (sharded save / resume) and ``[fault]`` (process-group timeout,
+heartbeat).
+"""
+from __future__ import annotations
+
+import tomllib
+from pathlib import Path
+from typing import Any, Literal
+
+from pydantic import BaseModel, ConfigDict, Field, NonNegativeInt, PositiveInt, model_validator
+
+DTypeName = Literal["float16", "float32", "bfloat16"]
+
+
+class _Strict(BaseModel):
+    """Base for every table: extra keys are an error, torch dtypes may be assigned later."""
+
+    model_config = ConfigDict(extra="forbid", arbitrary_types_allowed=True)
+
+
+class DataConfig(_Strict):
+    num_workers: PositiveInt
+    train_tokens_path: str
+    val_tokens_path: str
+
+
+class OptimizerConfig(_Strict):
+    type: str
+    lr: float
+
+
+class TokenEmbeddingConfig(_Strict):
+    pass
+
+
+class PositionalEmbeddingConfig(_Strict):
+    pass
+
+
+class RuntimeConfig(_Strict):
+    """Parallel layout of one run (reference: src/config.py:42-57)."""
+
+    name: str
+    reducer: str = "v0"  # informational only, never branched on
+    bucket_size: int = 25  # MiB per gradient bucket
+    num_microbatches: int = 1
+    dp_size: int = 1
+    pp_size: int = 1
+    ep_size: int = 1
+    num_expert: PositiveInt = 1  # mirrored from model.num_experts by AppConfig
+
+
+class ProfilerConfig(_Strict):
+    enabled: bool = False
+    wait_steps: NonNegativeInt = 2
+    warmup_steps: NonNegativeInt = 2
+    active_steps: NonNegativeInt = 6
+    record_shapes: bool = True
+    profile_memory: bool = True
+    with_stack: bool = False
+    with_flops: bool = False
+
+    @model_validator(mode="after")
+    def _active_steps_positive(self) -> "ProfilerConfig":
+        if self.enabled and self.active_steps == 0:
+            raise ValueError("profiler.active_steps must be positive when profiler.enabled=true")
+        return self
+
+
+class HardwareConfig(_Strict):
+    peak_flops_tflops_per_gpu: float = 0.0
+
+
+class ModelConfig(_Strict):
+    vocab_size: PositiveInt
+    d_model: PositiveInt
+    d_head: PositiveInt
+    n_heads: PositiveInt
+    n_layers: PositiveInt
+    max_seq_len: PositiveInt
+    ffn_in: PositiveInt
+    num_experts: PositiveInt
+    top_k: PositiveInt
+    token_embedding: TokenEmbeddingConfig = Field(default_factory=TokenEmbeddingConfig)
+    positional_embedding: PositionalEmbeddingConfig = Field(
+        default_factory=PositionalEmbeddingConfig
+    )
+    moe_backend: str = "torch"
+    dtype: DTypeName = "float32"
+    moe_router_dtype: DTypeName = "float32"
+    router_alpha: float
+
+    @model_validator(mode="after")
+    def _even_width(self) -> "ModelConfig":
+        if self.d_model % 2 != 0:
+            raise ValueError(
+                "model.d_model must be even when using sinusoidal positional embeddings"
+            )
+        return self
+
+
+class TrainerConfig(_Strict):
+    device_id: NonNegativeInt
+    eval_every_step: int
+    per_device_batch_size: PositiveInt
+    seed: PositiveInt
+
+
+class CheckpointConfig(_Strict):
+    """Sharded checkpointing (no counterpart in the reference, which never saves)."""
+
+    dir: str = ""
+    every_steps: NonNegativeInt = 0  # 0 disables periodic saves
+    resume: bool = False
+
+
+class FaultConfig(_Strict):
+    """Host-side failure detection (no counterpart in the reference)."""
+
+    pg_timeout_s: float = 600.0
+    heartbeat_dir: str = ""
+    heartbeat_stale_s: float = 120.0
+
+
+class AppConfig(_Strict):
+    run_name: str
+    max_steps: PositiveInt
+    model: ModelConfig
+    trainer: TrainerConfig
+    data: DataConfig
+    optim: OptimizerConfig
+    runtime: RuntimeConfig
+    profiler: ProfilerConfig = Field(default_factory=ProfilerConfig)
+    hardware: HardwareConfig = Field(default_factory=HardwareConfig)
+    checkpoint: CheckpointConfig = Field(default_factory=CheckpointConfig)
+    fault: FaultConfig = Field(default_factory=FaultConfig)
+    track_backward_time: bool = False
+
+    @model_validator(mode="before")
+    @classmethod
+    def _mirror_expert_count(cls, raw: Any) -> Any:
+        """runtime.num_expert always equals model.num_experts (src/config.py:138-153)."""
+        if not isinstance(raw, dict):
+            return raw
+        model, runtime = raw.get("model"), raw.get("runtime")
+        if not isinstance(model, dict) or not isinstance(runtime, dict):
+            return raw
+        out = dict(raw)
+        out["runtime"] = {**runtime, "num_expert": model.get("num_experts")}
+        return out
+
+
+def resolve_config_path(path: str | Path) -> Path:
+    """Return ``path`` if it exists, else ``configs/<path>`` (src/config.py:156-165)."""
+    direct = Path(path)
+    if direct.exists():
+        return direct
+    fallback = Path("configs") / direct
+    if fallback.exists():
+        return fallback
+    raise FileNotFoundError(f"Could not find config file at '{path}' or '{fallback}'")
+
+
+def load_config(path: str | Path) -> AppConfig:
+    with resolve_config_path(path).open("rb") as fh:
+        return AppConfig.model_validate(tomllib.load(fh))

@@ -1,0 +1,92 @@
+"""Build and load the `nanotitan_cuda` extension (sm_100a only, in-tree).
+
+`build_extension()` compiles every source under `nanotitan_b200/csrc` with
+``-gencode arch=compute_100a,code=sm_100a`` into `nanotitan_b200/csrc/_build/`
+(nvcc cross-compiles, no GPU needed).  `get_ext()` imports the built shared object
+from that folder; it never falls back to another implementation: on a machine with
+a GPU a missing extension is an error, not a silent slow path.
+"""
+from __future__ import annotations
+
+import importlib.util
+import os
+import sys
+from functools import lru_cache
+from pathlib import Path
+from types import ModuleType
+
+CSRC = Path(__file__).resolve().parent.parent / "csrc"
+BUILD_DIR = CSRC / "_build"
+EXT_NAME = "nanotitan_cuda"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "--use_fast_math", "-std=c++17",
+    "--expt-relaxed-constexpr", "--expt-extended-lambda",
+    "-Xptxas", "-v",
+    "-U__CUDA_NO_HALF_OPERATORS__", "-U__CUDA_NO_HALF_CONVERSIONS__",
+    "-U__CUDA_NO_BFLOAT16_CONVERSIONS__", "-U__CUDA_NO_HALF2_OPERATORS__",
+]
+
+
+def sources() -> list[str]:
+    found = sorted(str(p) for p in CSRC.rglob("*.cu") if "_build" not in p.parts)
+    found += sorted(str(p) for p in CSRC.rglob("*.cpp") if "_build" not in p.parts and "standalone" not in p.parts)
+    return found
+
+
+def so_path() -> Path | None:
+    hits = sorted(BUILD_DIR.glob(f"{EXT_NAME}*.so"))
+    return hits[0] if hits else None
+
+
+def build_extension(verbose: bool = False) -> Path:
+    """Compile (incrementally, with ninja) and return the path of the shared object."""
+    from torch.utils import cpp_extension
+
+    BUILD_DIR.mkdir(parents=True, exist_ok=True)
+    os.environ.setdefault("MAX_JOBS", str(min(8, os.cpu_count() or 4)))
+    # The arch comes from NVCC_FLAGS; keep torch from appending its own list for the visible GPU.
+    os.environ["TORCH_CUDA_ARCH_LIST"] = "10.0a"
+    cpp_extension.load(
+        name=EXT_NAME,
+        sources=sources(),
+        extra_include_paths=[str(CSRC), str(CSRC / "runtime")],
+        extra_cflags=["-O3", "-std=c++17"],
+        extra_cuda_cflags=NVCC_FLAGS,
+        extra_ldflags=["-lcuda"],
+        build_directory=str(BUILD_DIR),
+        verbose=verbose,
+        is_python_module=False,
+    )
+    path = so_path()
+    if path is None:
+        raise RuntimeError(f"build finished but no {EXT_NAME}*.so in {BUILD_DIR}")
+    get_ext.cache_clear()
+    return path
+
+
+def have_ext() -> bool:
+    return so_path() is not None
+
+
+@lru_cache
+def get_ext() -> ModuleType:
+    path = so_path()
+    if path is None:
+        raise RuntimeError(
+            f"The {EXT_NAME} extension is not built. Run `python -c 'import __graft_entry__ as g; "
+            "g.build()'` (or nanotitan_b200.ops.ext.build_extension()) first."
+        )
+    import torch  # noqa: F401  (libtorch symbols must be loaded before the extension)
+
+    spec = importlib.util.spec_from_file_location(EXT_NAME, path)
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    sys.modules[EXT_NAME] = module
+    return module
+
+
+def native(t) -> bool:
+    """True when `t` lives on a GPU, where the CUDA kernels are the code path."""
+    return t.is_cuda

@@ -1,0 +1,232 @@
+"""GPipe pipeline step: all microbatch forwards, then all backwards in reverse order.
+
+Contract of the reference's `PipelineParallel` (src/parallel/pp.py:17-210): it wraps
+every run (pp_size 1 included) and owns loss computation, `zero_grad`, the reducers'
+finalisation, `optimizer.step()` and the step metrics.  Losses are scaled as in the
+reference: cross-entropy and the per-stage mean load-balancing loss (divided by
+pp_size) are both divided by the number of microbatches; each stage back-propagates
+its own auxiliary loss locally; gradient sync fires only on the last backward.
+
+What differs: stage-boundary activations travel with non-blocking NCCL `isend` /
+`irecv` whose receives are all posted before the first forward (and before the first
+backward), so transfers of microbatch i+1 overlap the compute of microbatch i; the
+last stage computes the loss with the fused unembed + cross-entropy op; times are
+CUDA-event device times; and there is one device sync per step, at its end.
+"""
+from __future__ import annotations
+
+import logging
+import time
+
+import torch
+import torch.distributed as dist
+
+from nanotitan_b200.dist_env import local_device
+from nanotitan_b200.metrics import HistogramMetric, ScalarMetric
+from nanotitan_b200.profiler import nvtx_range
+from nanotitan_b200.utils import resolve_dtype
+
+logger = logging.getLogger(__name__)
+
+
+class _Clock:
+    """Device time (CUDA events) on GPUs, host time on CPU."""
+
+    def __init__(self, device: torch.device):
+        self.cuda = device.type == "cuda"
+        self.marks: dict[str, object] = {}
+
+    def mark(self, name: str) -> None:
+        if self.cuda:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.marks[name] = ev
+        else:
+            self.marks[name] = time.perf_counter()
+
+    def seconds(self, start: str, end: str) -> float:
+        a, b = self.marks[start], self.marks[end]
+        if self.cuda:
+            return a.elapsed_time(b) / 1e3
+        return b - a
+
+
+class PipelineParallel:
+    def __init__(self, cfg, dim, reducers: dict):
+        self.cfg = cfg
+        self.dim = dim
+        self.device = local_device()
+        self.reducers = reducers
+        self.stage_inputs: list[torch.Tensor] = []
+        self.stage_outputs: list[torch.Tensor] = []
+        self._pending: list = []
+        self.use_fused_loss = True
+
+    # ------------------------------------------------------------------ helpers
+    def synchronize_device(self) -> None:
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+
+    def prepare_microbatch(self, x, y):
+        n = self.cfg.runtime.num_microbatches
+        assert x.shape[0] % n == 0
+        return x.chunk(chunks=n), y.chunk(chunks=n)
+
+    def _boundary_buffer(self) -> torch.Tensor:
+        return torch.empty(
+            (self.microbatch_size, self.cfg.model.max_seq_len, self.cfg.model.d_model),
+            device=self.device,
+            dtype=resolve_dtype(self.cfg.model.dtype),
+        )
+
+    def _post_recvs(self, src: int, count: int):
+        """Pre-post `count` receives from `src`; returns [(buffer, work)] in arrival order."""
+        posted = []
+        for _ in range(count):
+            buf = self._boundary_buffer()
+            posted.append((buf, dist.irecv(buf, src=src, group=self.dim.pp_group)))
+        return posted
+
+    def _send(self, tensor: torch.Tensor, dst: int) -> None:
+        self._pending.append((tensor, dist.isend(tensor.contiguous(), dst=dst, group=self.dim.pp_group)))
+
+    def _zero_grad(self, optimizer) -> None:
+        owned = {id(p) for r in self.reducers.values() for p in r.params}
+        for r in self.reducers.values():
+            r.zero_grad()
+        for group in optimizer.param_groups:
+            for p in group["params"]:
+                if id(p) not in owned:
+                    p.grad = None
+
+    # ------------------------------------------------------------------ step
+    def train_step(self, model, batch, optimizer):
+        x, y = batch
+        n_mb = self.cfg.runtime.num_microbatches
+        microbatch_x, microbatch_y = self.prepare_microbatch(x, y)
+        self.microbatch_size = x.shape[0] // n_mb
+        first, last = self.dim.is_pp_first_stage, self.dim.is_pp_last_stage
+        clock = _Clock(self.device)
+        host_start = time.perf_counter()
+        clock.mark("start")
+
+        self._zero_grad(optimizer)
+        ce_losses, aux_losses, stats_list = [], [], []
+        with nvtx_range("forward_pass"):
+            recvs = [] if first else self._post_recvs(self.dim.prev_pp_rank, n_mb)
+            for i, (mb_x, mb_y) in enumerate(zip(microbatch_x, microbatch_y, strict=False)):
+                if first:
+                    mb_x = mb_x.to(self.device, non_blocking=True)
+                else:
+                    mb_x, work = recvs[i]
+                    work.wait()
+                    mb_x.requires_grad_()
+                    self.stage_inputs.append(mb_x)
+                if last:
+                    mb_y = mb_y.to(self.device, non_blocking=True)
+                    if self.use_fused_loss and hasattr(model, "forward_loss"):
+                        loss, stats = model.forward_loss(mb_x, mb_y)
+                    else:
+                        logits, stats = model(mb_x)
+                        loss = torch.nn.functional.cross_entropy(
+                            logits.reshape(-1, logits.size(-1)).float(), mb_y.reshape(-1)
+                        )
+                    ce_losses.append(loss)
+                else:
+                    out, stats = model(mb_x)
+                    self.stage_outputs.append(out)
+                    self._send(out.detach(), self.dim.next_pp_rank)
+                    ce_losses.append(None)
+                aux = torch.stack([s.aux_loss for s in stats]).mean() / self.dim.pp_size
+                aux_losses.append(aux)
+                stats_list.append(stats)
+        clock.mark("forward_end")
+
+        with nvtx_range("backward_pass"):
+            grads_in = [] if last else self._post_recvs(self.dim.next_pp_rank, n_mb)
+            for step_idx, mb in enumerate(reversed(range(n_mb))):
+                for reducer in self.reducers.values():
+                    reducer.backward_grad_sync = mb == 0
+                ce = ce_losses[mb] / n_mb if last else None
+                aux = aux_losses[mb] / n_mb
+                incoming = None if last else grads_in[step_idx]
+                self.backward(ce, aux, model, mb, incoming)
+            for reducer in self.reducers.values():
+                reducer.prepare_missing_grad()
+            self.finalize_backward()
+        clock.mark("backward_end")
+
+        with nvtx_range("optimizer_step"):
+            optimizer.step()
+        clock.mark("end")
+        for _, work in self._pending:
+            work.wait()
+        self._pending = []
+
+        # One host read for all loss values (also the step's only device sync).
+        if last:
+            ce_sum = torch.stack([c.detach().float() for c in ce_losses]).sum()
+            aux_sum = torch.stack([a.detach().float() for a in aux_losses]).sum()
+            ce_sum, aux_sum = torch.stack([ce_sum, aux_sum]).tolist()
+        else:
+            ce_sum = aux_sum = 0.0
+        self.synchronize_device()
+        step_time = clock.seconds("start", "end")
+        metrics = {
+            "train/ce_loss": ScalarMetric(ce_sum / n_mb, reduce="sum"),
+            "train/lb_loss": ScalarMetric(aux_sum / n_mb, reduce="sum"),
+            # same precedence as the reference: sum(ce) + sum(aux)/n (src/parallel/pp.py:124)
+            "train/total_loss": ScalarMetric(ce_sum + aux_sum / n_mb if last else 0.0, reduce="sum"),
+            "time/step_time": ScalarMetric(step_time, reduce="max"),
+            "time/forward_time": ScalarMetric(clock.seconds("start", "forward_end"), reduce="max"),
+            "time/backward_time": ScalarMetric(
+                clock.seconds("forward_end", "backward_end"), reduce="max"
+            ),
+            "time/host_step_time": ScalarMetric(time.perf_counter() - host_start, reduce="max"),
+        }
+        metrics.update(self._moe_route_fraction_metrics(model, stats_list))
+        return metrics
+
+    def backward(self, ce_loss, moe_aux_loss, model, microbatch_idx, incoming=None) -> None:
+        if self.dim.is_pp_last_stage:
+            torch.autograd.backward([ce_loss, moe_aux_loss])
+        else:
+            out = self.stage_outputs[microbatch_idx]
+            grad_buf, work = incoming
+            work.wait()
+            torch.autograd.backward([out, moe_aux_loss], [grad_buf, torch.ones_like(moe_aux_loss)])
+        if not self.dim.is_pp_first_stage:
+            self._send(self.stage_inputs[microbatch_idx].grad, self.dim.prev_pp_rank)
+
+    def finalize_backward(self) -> None:
+        self.stage_inputs = []
+        self.stage_outputs = []
+        for reducer in self.reducers.values():
+            reducer.finalize_backward()
+
+    # ------------------------------------------------------------------ metrics
+    def _moe_route_fraction_metrics(self, model, moe_stats_list) -> dict:
+        """Per global layer, the fraction of assignments each expert received; stages that do
+        not own a layer contribute zeros so a SUM over ranks gives the DP mean."""
+        metrics = {}
+        local = {}
+        if moe_stats_list and moe_stats_list[0]:
+            n_local = len(moe_stats_list[0])
+            counts = torch.stack(
+                [
+                    torch.stack([mb[i].tokens_per_expert.detach().float() for i in range(n_local)])
+                    for mb in moe_stats_list
+                ]
+            ).sum(dim=0)  # [local layers, E]
+            fracs = (counts / counts.sum(dim=1, keepdim=True).clamp_min(1.0)).cpu()
+            for i in range(n_local):
+                local[model.spec.layer_start + i] = fracs[i]
+        # DP is folded over EP: dp*ep ranks per stage see different data.
+        replicas = self.dim.dp_size * self.dim.ep_size
+        for layer in range(self.cfg.model.n_layers):
+            frac = local.get(layer)
+            value = torch.zeros(self.cfg.model.num_experts, dtype=torch.float32)
+            if frac is not None:
+                value = frac / replicas
+            metrics[f"moe/layer_{layer:02d}/route_frac_dist"] = HistogramMetric(value, reduce="sum")
+        return metrics

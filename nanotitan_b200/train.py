@@ -1,0 +1,176 @@
+"""Training entrypoint: ``torchrun ... -m nanotitan_b200.train @cfg.toml [--log.level L]``.
+
+Same flow as the reference's `main()` (src/train.py:81-226): load the TOML, set up the
+process group and the DP x PP x EP layout, build this rank's model shard, wrap it in
+the data-parallel reducers and the GPipe step, then loop over the sharded loader
+logging the reference's metric names.  It also runs as a single process with no
+launcher, on CPU (gloo) as well as GPUs (NCCL), and adds `--resume`, periodic sharded
+checkpoints, a per-step heartbeat, MFU and gradient-norm metrics.
+"""
+from __future__ import annotations
+
+import argparse
+import logging
+
+import torch
+
+from nanotitan_b200.data.dataset import PackedTokenDataset, SyntheticTokenDataset
+from nanotitan_b200.dist_env import cleanup, get_world_size, init_distributed, local_device
+from nanotitan_b200.metrics import MetricsLogger, ScalarMetric, reduce_metrics
+from nanotitan_b200.models.model import NanoTitanModel
+from nanotitan_b200.models.utils import get_model_shard_specs
+from nanotitan_b200.optim import setup_optimizer
+from nanotitan_b200.parallel import DataParallel, PipelineParallel
+from nanotitan_b200.parallel_dims import get_parallel_dims
+from nanotitan_b200.profiler import build_profiler
+from nanotitan_b200.utils import load_run_config, reduce_scalars, seed_everything, setup_logging
+from nanotitan_b200.utils.checkpoint import latest_checkpoint, load_checkpoint, save_checkpoint
+from nanotitan_b200.utils.heartbeat import Heartbeat
+
+logger = logging.getLogger(__name__)
+
+__all__ = ["main", "parse_args", "reduce_metrics", "build_training", "model_flops_per_token"]
+
+
+def parse_args(argv=None) -> argparse.Namespace:
+    parser = argparse.ArgumentParser(description="Train a NanoTitan model from a TOML config.")
+    parser.add_argument("--single_gpu", action="store_true",
+                        help="Accepted for compatibility; a 1-process run needs no flag.")
+    parser.add_argument("--log.level", default="INFO", dest="log_level",
+                        help="Python logging level, e.g. DEBUG, INFO, WARNING.")
+    parser.add_argument("--resume", default="", help="Checkpoint directory to resume from.")
+    parser.add_argument("--synthetic-data", action="store_true",
+                        help="Uniform-random token ids instead of the token file.")
+    parser.add_argument("config", help="TOML config path, optionally prefixed with '@'.")
+    return parser.parse_args(argv)
+
+
+def model_flops_per_token(cfg, active_params: float) -> float:
+    """6 * active matmul parameters + causal attention (fwd + bwd), per token."""
+    m = cfg.model
+    embed = m.vocab_size * m.d_model  # the lookup table does no matmul work
+    attn = 6 * m.n_layers * m.max_seq_len * m.n_heads * m.d_head  # 12*S*H*Dh/2 (causal)
+    return 6.0 * (active_params - embed) + attn
+
+
+def build_training(cfg, dims):
+    """Model shard + DP reducers + GPipe step + optimizer for this rank."""
+    spec = get_model_shard_specs(dims, cfg)
+    model = NanoTitanModel.from_specs(cfg.model, spec)
+    dp = DataParallel(cfg, dims)
+    dp.prepare_model(model)
+    pp = PipelineParallel(cfg, dims, dp.get_reducers())
+    optimizer = setup_optimizer(cfg.optim, model)
+    if hasattr(optimizer, "bind_reducers"):
+        optimizer.bind_reducers(dp.get_reducers())
+    return model, dp, pp, optimizer
+
+
+def main(argv=None) -> None:
+    args = parse_args(argv)
+    setup_logging(args.log_level)
+    cfg = load_run_config(args.config)
+    init_distributed(timeout_s=cfg.fault.pg_timeout_s)
+    world_size = get_world_size()
+    assert world_size == cfg.runtime.dp_size * cfg.runtime.pp_size * cfg.runtime.ep_size, (
+        f"world size {world_size} != dp*pp*ep"
+    )
+    assert cfg.model.n_layers % cfg.runtime.pp_size == 0
+    assert cfg.trainer.per_device_batch_size % cfg.runtime.num_microbatches == 0
+
+    seed_everything(cfg.trainer.seed)
+    dims = get_parallel_dims(cfg.runtime)
+    logger.debug("rank %d: %r", dims.global_rank, dims)
+    device = local_device()
+    model, dp, pp, optimizer = build_training(cfg, dims)
+
+    metrics_logger = MetricsLogger(cfg.run_name) if dims.local_rank == 0 else None
+    if args.synthetic_data:
+        n_seq = cfg.trainer.per_device_batch_size * dims.data_world_size * cfg.max_steps
+        train_dataset = SyntheticTokenDataset(
+            cfg.model.vocab_size, cfg.model.max_seq_len, n_seq, cfg.trainer.seed
+        )
+    else:
+        train_dataset = PackedTokenDataset(cfg.data.train_tokens_path, cfg.model.max_seq_len)
+    train_loader = dp.prepare_trainloader(train_dataset)
+
+    counts = torch.tensor(
+        [model.total_parameter_count(), float(model.active_parameter_count())],
+        dtype=torch.float64, device=device,
+    )
+    reduce_scalars(counts, dims.pp_group)
+    total_params, active_params = counts.tolist()
+    if dims.global_rank == 0:
+        logger.info("Number of parameters: %.2fM total, %.2fM active",
+                    total_params / 1e6, active_params / 1e6)
+        logger.info("Model parameters and activations will be in %s datatype", cfg.model.dtype)
+
+    step = 0
+    tokens_seen = 0
+    resume_dir = args.resume or (cfg.checkpoint.dir if cfg.checkpoint.resume else "")
+    if resume_dir:
+        found = latest_checkpoint(resume_dir)
+        if found is not None:
+            state = load_checkpoint(found, model, optimizer, dims)
+            step, tokens_seen = state["step"], state["tokens_seen"]
+            logger.info("resumed from %s at step %d", found, step)
+
+    heartbeat = Heartbeat(cfg.fault.heartbeat_dir, dims.global_rank) if cfg.fault.heartbeat_dir else None
+    profiler = build_profiler(cfg.run_name, cfg.profiler, dims)
+    flops_per_token = model_flops_per_token(cfg, active_params)
+    peak = cfg.hardware.peak_flops_tflops_per_gpu * 1e12
+    # data is sharded over dp*ep ranks (the reference counts dp only, src/train.py:157)
+    tokens_per_step = cfg.trainer.per_device_batch_size * dims.data_world_size * cfg.model.max_seq_len
+    logger.info("Attempting to begin training")
+    try:
+        epoch = 0
+        with profiler as prof:
+            while step < cfg.max_steps:
+                if hasattr(train_loader.sampler, "set_epoch"):
+                    train_loader.sampler.set_epoch(epoch)
+                progressed = False
+                for batch in train_loader:
+                    progressed = True
+                    metrics = pp.train_step(model, batch, optimizer)
+                    tokens_seen += tokens_per_step
+                    metrics["train/tokens_per_step"] = ScalarMetric(tokens_per_step, reduce="none")
+                    metrics["train/total_tokens_seen"] = ScalarMetric(tokens_seen, reduce="none")
+                    if hasattr(optimizer, "last_grad_norm"):
+                        metrics["train/grad_norm"] = ScalarMetric(optimizer.last_grad_norm(), reduce="max")
+                    metrics = reduce_metrics(metrics, device)
+                    metrics["train/tokens_per_second"] = (
+                        metrics["train/tokens_per_step"] / metrics["time/step_time"]
+                    )
+                    metrics["train/ce_loss"] = metrics["train/ce_loss"] / dims.data_world_size
+                    metrics["train/lb_loss"] = metrics["train/lb_loss"] / dims.data_world_size
+                    if peak > 0:
+                        metrics["perf/mfu"] = (
+                            metrics["train/tokens_per_second"] * flops_per_token / (peak * world_size)
+                        )
+                    if dims.local_rank == 0:
+                        logger.info("step %d | ce %.4f | lb %.4f | %.0f tok/s | %.1f ms",
+                                    step, metrics["train/ce_loss"], metrics["train/lb_loss"],
+                                    metrics["train/tokens_per_second"], 1e3 * metrics["time/step_time"])
+                        metrics_logger.log(step=step, metrics=metrics)
+                    step += 1
+                    prof.step()
+                    if heartbeat is not None:
+                        heartbeat.beat(step)
+                    every = cfg.checkpoint.every_steps
+                    if cfg.checkpoint.dir and every and step % every == 0:
+                        save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg)
+                    if step >= cfg.max_steps:
+                        break
+                epoch += 1
+                if not progressed:
+                    raise RuntimeError("the training loader produced no batch (dataset too small)")
+        if cfg.checkpoint.dir:
+            save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg)
+    finally:
+        if metrics_logger is not None:
+            metrics_logger.close()
+        cleanup()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,147 @@
+"""Sharded checkpoints: one file per rank plus a manifest, written atomically.
+
+The reference never saves anything; the layout to honour is its `state_dict()` key
+scheme (stage-local `blocks.<i>` indices, local expert slices).  A shard file holds
+that state dict (tensors cloned out of the flat buckets they view into), the
+optimizer state, step, token count, RNG states and the rank's coordinates.
+`consolidate` rebuilds the single-process view (global layer indices, all experts)
+so weights can be exchanged with a reference run.
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+from pathlib import Path
+
+import torch
+
+_STEP_DIR = re.compile(r"step_(\d+)$")
+
+
+def _rank_file(step_dir: Path, rank: int) -> Path:
+    return step_dir / f"rank_{rank:05d}.pt"
+
+
+def save_checkpoint(directory, step: int, tokens_seen: int, model, optimizer, dims, cfg=None) -> Path:
+    step_dir = Path(directory) / f"step_{step:08d}"
+    step_dir.mkdir(parents=True, exist_ok=True)
+    payload = {
+        "model": {k: v.detach().clone().cpu() for k, v in model.state_dict().items()},
+        "optimizer": optimizer.state_dict() if optimizer is not None else None,
+        "step": step,
+        "tokens_seen": tokens_seen,
+        "rng": {
+            "torch": torch.get_rng_state(),
+            "cuda": torch.cuda.get_rng_state_all() if torch.cuda.is_available() else None,
+        },
+        "coords": {
+            "global_rank": dims.global_rank, "dp_rank": dims.dp_rank, "pp_rank": dims.pp_rank,
+            "ep_rank": dims.ep_rank, "dp_size": dims.dp_size, "pp_size": dims.pp_size,
+            "ep_size": dims.ep_size,
+        },
+        "spec": {
+            "layer_start": model.spec.layer_start, "layer_end": model.spec.layer_end,
+            "start_expert_id": model.spec.start_expert_id, "end_expert_id": model.spec.end_expert_id,
+            "has_token_embed": model.spec.has_token_embed, "has_unembed_head": model.spec.has_unembed_head,
+        },
+    }
+    target = _rank_file(step_dir, dims.global_rank)
+    tmp = target.with_suffix(".tmp")
+    torch.save(payload, tmp)
+    os.replace(tmp, target)
+    if dims.global_rank == 0:
+        manifest = {"step": step, "tokens_seen": tokens_seen, "world_size": dims.world_size,
+                    "config": cfg.model_dump(mode="json") if cfg is not None and hasattr(cfg, "model_dump") else None}
+        mtmp = step_dir / "manifest.tmp"
+        mtmp.write_text(json.dumps(manifest, indent=2, default=str))
+        os.replace(mtmp, step_dir / "manifest.json")
+    return step_dir
+
+
+def latest_checkpoint(directory) -> Path | None:
+    """Newest `step_*` folder that has a manifest (i.e. whose save completed on rank 0)."""
+    root = Path(directory)
+    if _STEP_DIR.search(root.name) and (root / "manifest.json").exists():
+        return root
+    best = None
+    for child in root.glob("step_*"):
+        m = _STEP_DIR.search(child.name)
+        if m and (child / "manifest.json").exists():
+            if best is None or int(m.group(1)) > best[0]:
+                best = (int(m.group(1)), child)
+    return None if best is None else best[1]
+
+
+def load_checkpoint(step_dir, model, optimizer, dims) -> dict:
+    payload = torch.load(_rank_file(Path(step_dir), dims.global_rank), map_location="cpu", weights_only=False)
+    with torch.no_grad():
+        own = model.state_dict()
+        for key, value in payload["model"].items():
+            own[key].copy_(value)  # in place: parameters may view into flat buckets
+    if optimizer is not None and payload["optimizer"] is not None:
+        optimizer.load_state_dict(payload["optimizer"])
+    torch.set_rng_state(payload["rng"]["torch"])
+    if payload["rng"]["cuda"] is not None and torch.cuda.is_available():
+        torch.cuda.set_rng_state_all(payload["rng"]["cuda"])
+    return {"step": payload["step"], "tokens_seen": payload["tokens_seen"]}
+
+
+def consolidate(step_dir) -> dict[str, torch.Tensor]:
+    """Merge the dp_rank-0 shards of every (pp, ep) coordinate into the state dict a
+    single-process model (pp_size = ep_size = 1) would have."""
+    shards = [torch.load(p, map_location="cpu", weights_only=False) for p in sorted(Path(step_dir).glob("rank_*.pt"))]
+    shards = [s for s in shards if s["coords"]["dp_rank"] == 0]
+    merged: dict[str, torch.Tensor] = {}
+    expert_parts: dict[str, dict[int, torch.Tensor]] = {}
+    for s in shards:
+        shift = (s["spec"]["layer_start"] + 1) - (1 if s["spec"]["has_token_embed"] else 0)
+        for key, value in s["model"].items():
+            m = re.match(r"blocks\.(\d+)\.(.*)", key)
+            local, rest = int(m.group(1)), m.group(2)
+            if rest.startswith(("token_embed", "position_embed")):
+                new_key = f"blocks.0.{rest}"
+            else:
+                new_key = f"blocks.{local + shift}.{rest}"
+            if ".ffn.experts." in new_key:
+                expert_parts.setdefault(new_key, {})[s["coords"]["ep_rank"]] = value
+            elif s["coords"]["ep_rank"] == 0:
+                merged[new_key] = value
+    for key, parts in expert_parts.items():
+        merged[key] = torch.cat([parts[r] for r in sorted(parts)], dim=0)
+    return merged
+
+
+def shard_from_full(full_state: dict[str, torch.Tensor], spec) -> dict[str, torch.Tensor]:
+    """Inverse of `consolidate` for one rank: pick this stage's blocks (renumbered from the
+    stage-local index 0) and this rank's expert slice out of a single-process state dict."""
+    n_total = max(int(k.split(".")[1]) for k in full_state)  # index of the unembed block
+    out: dict[str, torch.Tensor] = {}
+    shift = (spec.layer_start + 1) - (1 if spec.has_token_embed else 0)
+    for key, value in full_state.items():
+        idx, rest = int(key.split(".")[1]), key.split(".", 2)[2]
+        if idx == 0:
+            if not spec.has_token_embed:
+                continue
+            local = 0
+        elif idx == n_total:
+            if not spec.has_unembed_head:
+                continue
+            local = idx - shift
+        else:
+            layer = idx - 1
+            if not (spec.layer_start <= layer < spec.layer_end):
+                continue
+            local = idx - shift
+        if ".ffn.experts." in key:
+            value = value[spec.start_expert_id : spec.end_expert_id]
+        out[f"blocks.{local}.{rest}"] = value
+    return out
+
+
+def load_full_state(model, full_state: dict[str, torch.Tensor]) -> None:
+    """Copy a single-process state dict into this rank's shard, in place."""
+    own = model.state_dict()
+    with torch.no_grad():
+        for key, value in shard_from_full(full_state, model.spec).items():
+            own[key].copy_(value)
