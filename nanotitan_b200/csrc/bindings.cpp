@@ -1,0 +1,47 @@
+// Python module `nanotitan_cuda`: the fourteen entry points of the reference's extension
+// (csrc/bindings.cpp:59-92 there, same names, argument orders and return conventions) plus
+// the kernels the framework itself calls.
+#include <torch/extension.h>
+
+#include "cuda_check.h"
+#include "kernels/ops.h"
+
+namespace py = pybind11;
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "nanotitan_b200 sm_100a kernels";
+  // ---- reference-compatible surface
+  m.def("random_op", &nt::random_op, "Zero vector of length x with t's options");
+  m.def("copy_scalar", &nt::copy_scalar, "Element-wise copy of n elements");
+  m.def("copy_vector", &nt::copy_vector, "16-byte vector copy");
+  m.def("peer_copy_scalar", &nt::peer_copy_scalar, "GPU-to-GPU copy over NVLink");
+  m.def("count_expert_kernel", &nt::count_expert_kernel, "Histogram of expert ids");
+  m.def("pack_tokens_kernel", &nt::pack_tokens_kernel, "Pack token rows into expert-major order");
+  m.def("combine_tokens_kernel", &nt::combine_tokens_kernel, "Gate-weighted combine of expert rows (fp32 out)");
+  m.def("combine_kernel_backward", &nt::combine_kernel_backward, "Backward of combine");
+  m.def("gemm_kernel", &nt::gemm_kernel, py::arg("A"), py::arg("B"), py::arg("implementation") = "tiled");
+  m.def("tiled_gemm_kernel", &nt::tiled_gemm_kernel);
+  m.def("naive_gemm_kernel", &nt::naive_gemm_kernel);
+  m.def("pack_kernel_backward", &nt::pack_kernel_backward, "Backward of pack");
+  m.def("grouped_gemm_kernel", &nt::grouped_gemm_kernel, "out[r] = X[r] . W[e(r)]");
+  m.def("bwd_grouped_gemm_dW_kernel", &nt::bwd_grouped_gemm_dW_kernel);
+  m.def("bwd_grouped_gemm_dX_kernel", &nt::bwd_grouped_gemm_dX_kernel);
+  // ---- framework kernels
+  m.def("gemm_tc", &nt::gemm_tc, py::arg("A"), py::arg("a_mn"), py::arg("Bs"), py::arg("b_mn"), py::arg("b_split"),
+        py::arg("Cs"), py::arg("mode") = 0, py::arg("offsets") = py::none(), py::arg("epilogue") = 0,
+        py::arg("accumulate") = false, py::arg("aux") = py::none(), py::arg("aux_out") = py::none(),
+        py::arg("force_bn") = 0);
+  m.def("layer_norm_fwd", &nt::layer_norm_fwd);
+  m.def("layer_norm_bwd", &nt::layer_norm_bwd);
+  m.def("cross_entropy_fwd_bwd", &nt::cross_entropy_fwd_bwd);
+  m.def("adamw_step", &nt::adamw_step);
+  m.def("router_topk", &nt::router_topk);
+  m.def("assign_slots", &nt::assign_slots);
+  m.def("pack_fwd", &nt::pack_fwd);
+  m.def("combine_fwd", &nt::combine_fwd);
+  m.def("combine_bwd", &nt::combine_bwd);
+  m.def("pack_bwd", &nt::pack_bwd);
+  m.def("read_status", &nt::read_status, py::arg("clear") = true, "[code, kernel, detail, count] of the device status word");
+  m.def("launch_count", [] { return static_cast<long long>(nt::launch_counter().load()); },
+        "Kernels of this library launched by this process");
+}

@@ -1,0 +1,259 @@
+// Host side of the tcgen05 GEMM: shape bookkeeping, TMA descriptors, tile-size choice, launch.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "cuda_check.h"
+#include "gemm_tc.cuh"
+#include "ops.h"
+#include "tma_desc.h"
+
+namespace nt {
+
+namespace {
+
+using gemm::Args;
+
+int dtype_code(const at::Tensor& t) {
+  if (t.scalar_type() == at::kBFloat16) return 1;
+  if (t.scalar_type() == at::kHalf) return 0;
+  TORCH_CHECK(false, "gemm_tc: operands must be bf16 or fp16, got ", t.scalar_type());
+}
+
+void check_operand(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.dim() == 2 || t.dim() == 3, name, " must be 2-D or 3-D");
+  TORCH_CHECK(t.stride(-1) == 1, name, " must have a contiguous last dim");
+  TORCH_CHECK(t.stride(-2) % 8 == 0, name, ": row stride must be a multiple of 8 elements (TMA needs 16-byte strides)");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, name, " must be 16-byte aligned");
+  if (t.dim() == 3) TORCH_CHECK(t.stride(0) % 8 == 0, name, ": group stride must be a multiple of 8 elements");
+}
+
+CUtensorMap map_a(const at::Tensor& a, bool a_mn) {
+  const uint64_t dims[2] = {static_cast<uint64_t>(a.size(1)), static_cast<uint64_t>(a.size(0))};
+  const uint64_t strides[1] = {static_cast<uint64_t>(a.stride(0)) * 2};
+  const uint32_t box[2] = {64, a_mn ? 64u : 128u};
+  return make_tma_desc(a.data_ptr(), 2, 2, dims, strides, box, true);
+}
+
+CUtensorMap map_b(const at::Tensor& b, bool b_mn, int box_rows) {
+  const bool three = b.dim() == 3;
+  const uint64_t groups = three ? b.size(0) : 1;
+  const uint64_t rows = b.size(-2), cols = b.size(-1);
+  const uint64_t ld = b.stride(-2);
+  const uint64_t gs = three ? static_cast<uint64_t>(b.stride(0)) : rows * ld;
+  const uint64_t dims[3] = {cols, rows, groups};
+  const uint64_t strides[2] = {ld * 2, gs * 2};
+  const uint32_t box[3] = {64, b_mn ? 64u : static_cast<uint32_t>(box_rows), 1};
+  return make_tma_desc(b.data_ptr(), 2, 3, dims, strides, box, true);
+}
+
+template <int BN, int EPI>
+void launch(const CUtensorMap& tA, const CUtensorMap (&tB)[3], const Args& args, int tiles, cudaStream_t stream) {
+  using S = gemm::Smem<BN>;
+  auto kernel = gemm::gemm_tc_kernel<BN, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL));
+    configured = true;
+  }
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  const int grid = std::max(1, std::min(tiles, sms));
+  kernel<<<grid, gemm::NUM_THREADS, S::TOTAL, stream>>>(tA, tB[0], tB[1], tB[2], args);
+  NT_KERNEL_CHECK();
+}
+
+int pick_bn(int m_tiles, int N, int sms) {
+  if (N <= 64) return 64;
+  double best = 1e30;
+  int best_bn = 128;
+  for (int bn : {256, 128}) {
+    const long long tiles = static_cast<long long>(m_tiles) * ((N + bn - 1) / bn);
+    const long long waves = (tiles + sms - 1) / sms;
+    const double cost = static_cast<double>(waves) * bn * (bn == 128 ? 1.06 : 1.0);
+    if (cost < best) { best = cost; best_bn = bn; }
+  }
+  return best_bn;
+}
+
+}  // namespace
+
+StatusWord* device_status_word() {
+  static StatusWord* words[64] = {nullptr};
+  int dev = 0;
+  NT_CUDA_CHECK(cudaGetDevice(&dev));
+  if (words[dev] == nullptr) {
+    NT_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&words[dev]), sizeof(StatusWord)));
+    NT_CUDA_CHECK(cudaMemset(words[dev], 0, sizeof(StatusWord)));
+  }
+  return words[dev];
+}
+
+std::vector<int64_t> read_status(bool clear) {
+  StatusWord host;
+  StatusWord* dev = device_status_word();
+  NT_CUDA_CHECK(cudaDeviceSynchronize());
+  NT_CUDA_CHECK(cudaMemcpy(&host, dev, sizeof(host), cudaMemcpyDeviceToHost));
+  if (clear) NT_CUDA_CHECK(cudaMemset(dev, 0, sizeof(StatusWord)));
+  return {host.code, host.kernel, host.detail, host.count};
+}
+
+// See ops.h for the contract.
+void gemm_tc(const at::Tensor& A, bool a_mn, const std::vector<at::Tensor>& Bs, bool b_mn, int64_t b_split,
+             const std::vector<at::Tensor>& Cs, int64_t mode, const c10::optional<at::Tensor>& offsets,
+             int64_t epilogue, bool accumulate, const c10::optional<at::Tensor>& aux,
+             const c10::optional<at::Tensor>& aux_out, int64_t force_bn) {
+  c10::cuda::CUDAGuard guard(A.device());
+  check_operand(A, "A");
+  TORCH_CHECK(A.dim() == 2, "A must be 2-D");
+  TORCH_CHECK(!Bs.empty() && Bs.size() <= 3 && !Cs.empty() && Cs.size() <= 3, "1..3 B sources and C destinations");
+  const int dt = dtype_code(A);
+  for (const auto& b : Bs) {
+    check_operand(b, "B");
+    TORCH_CHECK(dtype_code(b) == dt, "A and B must share a dtype");
+    TORCH_CHECK(b.sizes() == Bs[0].sizes(), "all B sources must have the same shape");
+  }
+  TORCH_CHECK((b_split == gemm::kBNone) == (Bs.size() == 1), "b_split and the number of B sources disagree");
+  TORCH_CHECK(b_split != gemm::kBDual || Bs.size() == 2, "dual-B needs exactly two sources");
+
+  Args args{};
+  args.mode = static_cast<int>(mode);
+  args.a_mn = a_mn;
+  args.b_mn = b_mn;
+  args.dtype = dt;
+  args.b_split = static_cast<int>(b_split);
+  args.accumulate = accumulate;
+  args.status = device_status_word();
+
+  const int64_t a_rows = A.size(0), a_cols = A.size(1);
+  const int64_t b_n = b_mn ? Bs[0].size(-1) : Bs[0].size(-2);  // per source
+  const int64_t b_k = b_mn ? Bs[0].size(-2) : Bs[0].size(-1);
+  const int nsrc = static_cast<int>(Bs.size());
+
+  if (mode == gemm::kGroupedK) {
+    TORCH_CHECK(a_mn && b_mn, "grouped-K needs MN-major A and B");
+    TORCH_CHECK(offsets.has_value(), "grouped modes need offsets");
+    TORCH_CHECK(Bs[0].dim() == 2 && Bs.size() == 1 && Bs[0].size(0) == a_rows, "grouped-K: A and B share the segmented rows");
+    args.M = static_cast<int>(a_cols);
+    args.N = static_cast<int>(b_n);
+    args.K = 0;
+  } else {
+    args.M = static_cast<int>(a_mn ? a_cols : a_rows);
+    const int64_t K = a_mn ? a_rows : a_cols;
+    args.K = static_cast<int>(K);
+    if (b_split == gemm::kBSplitN) {
+      args.N = static_cast<int>(b_n * nsrc);
+      args.b_split_size = static_cast<int>(b_n);
+      TORCH_CHECK(b_k == K, "B reduction extent ", b_k, " != A's ", K);
+    } else if (b_split == gemm::kBSplitK) {
+      args.N = static_cast<int>(b_n);
+      args.b_split_size = static_cast<int>(b_k);
+      TORCH_CHECK(b_k * nsrc == K, "sum of B reduction extents != A's K");
+      TORCH_CHECK(b_k % gemm::BK == 0, "K-split sources must be multiples of 64 deep");
+    } else {
+      args.N = static_cast<int>(b_n);
+      TORCH_CHECK(b_k == K, "B reduction extent ", b_k, " != A's ", K);
+    }
+  }
+  if (mode != gemm::kDense) {
+    TORCH_CHECK(offsets.has_value(), "grouped modes need offsets");
+    const auto& off = *offsets;
+    TORCH_CHECK(off.is_cuda() && off.scalar_type() == at::kInt && off.is_contiguous(), "offsets must be a contiguous int32 CUDA tensor");
+    args.G = static_cast<int>(off.numel() - 1);
+    TORCH_CHECK(args.G >= 1 && args.G <= gemm::MAX_GROUPS, "1..", gemm::MAX_GROUPS, " groups supported");
+    args.offsets = off.data_ptr<int>();
+    if (mode == gemm::kGroupedM) TORCH_CHECK(Bs[0].dim() == 3 && Bs[0].size(0) == args.G, "grouped-M: B must be [G, ., .]");
+  } else {
+    args.G = 1;
+    TORCH_CHECK(Bs[0].dim() == 2, "dense: B must be 2-D");
+  }
+
+  // ---- destinations
+  const int ndst = static_cast<int>(Cs.size());
+  const auto& C0 = Cs[0];
+  args.out_f32 = C0.scalar_type() == at::kFloat;
+  TORCH_CHECK(args.out_f32 || dtype_code(C0) == dt, "C must be fp32 or the operand dtype");
+  for (int i = 0; i < ndst; ++i) {
+    TORCH_CHECK(Cs[i].is_cuda() && Cs[i].stride(-1) == 1 && Cs[i].sizes() == C0.sizes() && Cs[i].strides() == C0.strides() &&
+                    Cs[i].scalar_type() == C0.scalar_type(), "C destinations must be same-shaped CUDA tensors");
+    args.C[i] = Cs[i].data_ptr();
+  }
+  args.ldc = C0.stride(-2);
+  int64_t c_cols_expected = args.N;
+  if (epilogue == gemm::kEpiSwigluFwd || epilogue == gemm::kEpiSwigluBwd) c_cols_expected = 2 * args.N;
+  if (ndst > 1) {
+    TORCH_CHECK(epilogue == gemm::kEpiStore && args.N % ndst == 0, "C split needs the store epilogue and N divisible by the count");
+    args.c_split_size = args.N / ndst;
+    c_cols_expected = args.c_split_size;
+  }
+  TORCH_CHECK(C0.size(-1) == c_cols_expected, "C has ", C0.size(-1), " columns, expected ", c_cols_expected);
+  if (mode == gemm::kGroupedK) {
+    TORCH_CHECK(C0.dim() == 3 && C0.size(0) == args.G && C0.size(1) == args.M, "grouped-K: C must be [G, M, N]");
+    args.c_group_stride = C0.stride(0);
+  } else {
+    TORCH_CHECK(C0.dim() == 2 && C0.size(0) >= args.M, "C must be [M, N]");
+  }
+
+  // ---- epilogue extras
+  if (epilogue == gemm::kEpiStore) {
+    if (aux.has_value()) {
+      TORCH_CHECK(mode != gemm::kGroupedK && aux->stride(-1) == 1 && dtype_code(*aux) == dt && aux->size(-1) == args.N, "bad residual");
+      args.R = aux->data_ptr();
+      args.ldr = aux->stride(-2);
+    }
+  } else if (epilogue == gemm::kEpiSwigluFwd) {
+    TORCH_CHECK(b_split == gemm::kBDual && aux_out.has_value() && !args.out_f32, "SwiGLU forward needs dual B and an H output");
+    TORCH_CHECK(aux_out->stride(-1) == 1 && aux_out->size(-1) == args.N && dtype_code(*aux_out) == dt, "bad H output");
+    args.C2 = aux_out->data_ptr();
+    args.ldc2 = aux_out->stride(-2);
+  } else {
+    TORCH_CHECK(aux.has_value() && aux->stride(-1) == 1 && aux->size(-1) == 2 * args.N && dtype_code(*aux) == dt && !args.out_f32,
+                "SwiGLU backward needs GV [rows, 2N]");
+    args.R = aux->data_ptr();
+    args.ldr = aux->stride(-2);
+  }
+
+  if (args.M == 0 || args.N == 0) return;
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  int m_tiles;
+  if (mode == gemm::kDense) m_tiles = (args.M + gemm::BM - 1) / gemm::BM;
+  else if (mode == gemm::kGroupedM) m_tiles = (args.M + gemm::BM - 1) / gemm::BM + args.G;  // upper bound
+  else m_tiles = args.G * ((args.M + gemm::BM - 1) / gemm::BM);
+
+  int bn = epilogue == gemm::kEpiSwigluFwd ? 256 : pick_bn(m_tiles, args.N, sms);
+  if (force_bn > 0) bn = static_cast<int>(force_bn);
+  TORCH_CHECK(bn == 64 || bn == 128 || bn == 256, "BN must be 64, 128 or 256");
+  if (b_split == gemm::kBSplitN) {
+    while (bn > 64 && args.b_split_size % bn != 0) bn /= 2;
+    TORCH_CHECK(args.b_split_size % bn == 0, "N-split sources must be a multiple of the tile width");
+  }
+  if (ndst > 1) {
+    while (bn > 64 && args.c_split_size % bn != 0) bn /= 2;
+    TORCH_CHECK(args.c_split_size % 32 == 0, "C split width must be a multiple of 32");
+  }
+  const int tn = epilogue == gemm::kEpiSwigluFwd ? bn / 2 : bn;
+  const int tiles = m_tiles * ((args.N + tn - 1) / tn);
+
+  const CUtensorMap tA = map_a(A, a_mn);
+  CUtensorMap tB[3];
+  const int box_rows = b_split == gemm::kBDual ? bn / 2 : bn;
+  for (int i = 0; i < 3; ++i) tB[i] = map_b(Bs[std::min(i, nsrc - 1)], b_mn, box_rows);
+
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+#define NT_LAUNCH(BN_, EPI_) launch<BN_, EPI_>(tA, tB, args, tiles, stream)
+  if (epilogue == gemm::kEpiSwigluFwd) {
+    TORCH_CHECK(bn == 256, "SwiGLU forward uses 256-wide tiles");
+    NT_LAUNCH(256, gemm::kEpiSwigluFwd);
+  } else if (epilogue == gemm::kEpiSwigluBwd) {
+    if (bn == 256) NT_LAUNCH(256, gemm::kEpiSwigluBwd);
+    else if (bn == 128) NT_LAUNCH(128, gemm::kEpiSwigluBwd);
+    else NT_LAUNCH(64, gemm::kEpiSwigluBwd);
+  } else {
+    if (bn == 256) NT_LAUNCH(256, gemm::kEpiStore);
+    else if (bn == 128) NT_LAUNCH(128, gemm::kEpiStore);
+    else NT_LAUNCH(64, gemm::kEpiStore);
+  }
+#undef NT_LAUNCH
+}
+
+}  // namespace nt

@@ -1,0 +1,194 @@
+// LayerNorm forward / backward with the model's semantics: biased variance, eps inside the
+// square root, affine gamma/beta (src/model/model.py:92-105 of the reference).
+// Memory-bound: one warp per row, 16-byte vector loads when the row allows, fp32 statistics.
+// Backward produces dx plus per-block partial sums of dgamma/dbeta that a second kernel folds
+// in a fixed order (no atomics, run-to-run deterministic).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "cuda_check.h"
+#include "ops.h"
+#include "vec.cuh"
+
+namespace nt {
+
+namespace {
+
+constexpr int LN_WARPS = 4;
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
+              float* __restrict__ mean_out, float* __restrict__ rstd_out, long long rows, int d, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * LN_WARPS + warp;
+  if (row >= rows) return;
+  const T* xr = x + row * d;
+  T* yr = y + row * d;
+  float sum = 0.f;
+  for (int c = lane * VEC; c < d; c += 32 * VEC) {
+    float v[VEC];
+    load_vec<T, VEC>(xr + c, v);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) sum += v[i];
+  }
+  const float mean = warp_sum(sum) / d;
+  float sq = 0.f;
+  for (int c = lane * VEC; c < d; c += 32 * VEC) {
+    float v[VEC];
+    load_vec<T, VEC>(xr + c, v);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) sq += (v[i] - mean) * (v[i] - mean);
+  }
+  const float rstd = rsqrtf(warp_sum(sq) / d + eps);
+  for (int c = lane * VEC; c < d; c += 32 * VEC) {
+    float v[VEC], g[VEC], b[VEC];
+    load_vec<T, VEC>(xr + c, v);
+    load_vec<T, VEC>(gamma + c, g);
+    load_vec<T, VEC>(beta + c, b);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[i] = (v[i] - mean) * rstd * g[i] + b[i];
+    store_vec<T, VEC>(yr + c, v);
+  }
+  if (lane == 0) {
+    mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
+}
+
+// dx = rstd * (gy - mean(gy) - xhat * mean(gy * xhat)), gy = gamma * dy.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+              const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx,
+              float* __restrict__ part_gamma, float* __restrict__ part_beta, long long rows, int d) {
+  extern __shared__ float acc[];  // [2][LN_WARPS][d]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* ag = acc + warp * d;
+  float* ab = acc + (LN_WARPS + warp) * d;
+  for (int c = lane; c < d; c += 32) { ag[c] = 0.f; ab[c] = 0.f; }
+  __syncwarp();
+  for (long long row = static_cast<long long>(blockIdx.x) * LN_WARPS + warp; row < rows;
+       row += static_cast<long long>(gridDim.x) * LN_WARPS) {
+    const T* xr = x + row * d;
+    const T* dyr = dy + row * d;
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = lane * VEC; c < d; c += 32 * VEC) {
+      float xv[VEC], gv[VEC], dv[VEC];
+      load_vec<T, VEC>(xr + c, xv);
+      load_vec<T, VEC>(gamma + c, gv);
+      load_vec<T, VEC>(dyr + c, dv);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float xhat = (xv[i] - mean) * rstd;
+        const float gy = gv[i] * dv[i];
+        s1 += gy;
+        s2 += gy * xhat;
+        ag[c + i] += dv[i] * xhat;
+        ab[c + i] += dv[i];
+      }
+    }
+    s1 = warp_sum(s1) / d;
+    s2 = warp_sum(s2) / d;
+    for (int c = lane * VEC; c < d; c += 32 * VEC) {
+      float xv[VEC], gv[VEC], dv[VEC];
+      load_vec<T, VEC>(xr + c, xv);
+      load_vec<T, VEC>(gamma + c, gv);
+      load_vec<T, VEC>(dyr + c, dv);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float xhat = (xv[i] - mean) * rstd;
+        xv[i] = rstd * (gv[i] * dv[i] - s1 - xhat * s2);
+      }
+      store_vec<T, VEC>(dx + row * d + c, xv);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float g = 0.f, b = 0.f;
+#pragma unroll
+    for (int w = 0; w < LN_WARPS; ++w) {
+      g += acc[w * d + c];
+      b += acc[(LN_WARPS + w) * d + c];
+    }
+    part_gamma[static_cast<long long>(blockIdx.x) * d + c] = g;
+    part_beta[static_cast<long long>(blockIdx.x) * d + c] = b;
+  }
+}
+
+// out[c] = sum over `parts` rows of in[p][c], rows visited in index order.
+__global__ void column_sum_kernel(const float* __restrict__ in, float* __restrict__ out, int parts, int d) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d) return;
+  float s = 0.f;
+  for (int p = 0; p < parts; ++p) s += in[static_cast<long long>(p) * d + c];
+  out[c] = s;
+}
+
+}  // namespace
+
+std::vector<at::Tensor> layer_norm_fwd(const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && gamma.is_contiguous() && beta.is_contiguous(), "layer_norm_fwd: contiguous CUDA tensors");
+  TORCH_CHECK(gamma.scalar_type() == x.scalar_type() && beta.scalar_type() == x.scalar_type(), "gamma/beta must share x's dtype");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int d = static_cast<int>(x.size(-1));
+  const long long rows = x.numel() / d;
+  auto y = at::empty_like(x);
+  auto mean = at::empty({rows}, x.options().dtype(at::kFloat));
+  auto rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  if (rows == 0) return {y, mean, rstd};
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  const unsigned grid = static_cast<unsigned>((rows + LN_WARPS - 1) / LN_WARPS);
+  NT_DISPATCH_FLOAT(x.scalar_type(), "layer_norm_fwd", [&] {
+    constexpr int V = 16 / sizeof(scalar_t);
+    const bool vec = d % V == 0 && is_aligned16(x.data_ptr()) && is_aligned16(gamma.data_ptr()) && is_aligned16(beta.data_ptr());
+    if (vec)
+      ln_fwd_kernel<scalar_t, V><<<grid, LN_WARPS * 32, 0, stream>>>(x.data_ptr<scalar_t>(), gamma.data_ptr<scalar_t>(), beta.data_ptr<scalar_t>(),
+          y.data_ptr<scalar_t>(), mean.data_ptr<float>(), rstd.data_ptr<float>(), rows, d, static_cast<float>(eps));
+    else
+      ln_fwd_kernel<scalar_t, 1><<<grid, LN_WARPS * 32, 0, stream>>>(x.data_ptr<scalar_t>(), gamma.data_ptr<scalar_t>(), beta.data_ptr<scalar_t>(),
+          y.data_ptr<scalar_t>(), mean.data_ptr<float>(), rstd.data_ptr<float>(), rows, d, static_cast<float>(eps));
+  });
+  NT_KERNEL_CHECK();
+  return {y, mean, rstd};
+}
+
+std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
+                                       const at::Tensor& mean, const at::Tensor& rstd) {
+  TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && x.is_contiguous() && gamma.is_contiguous(), "layer_norm_bwd: contiguous CUDA tensors");
+  TORCH_CHECK(dy.scalar_type() == x.scalar_type(), "dy and x must share a dtype");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int d = static_cast<int>(x.size(-1));
+  const long long rows = x.numel() / d;
+  auto dx = at::empty_like(x);
+  auto dgamma = at::zeros({d}, x.options().dtype(at::kFloat));
+  auto dbeta = at::zeros({d}, x.options().dtype(at::kFloat));
+  if (rows == 0) return {dx, dgamma, dbeta};
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  const int grid = static_cast<int>(std::min<long long>((rows + LN_WARPS - 1) / LN_WARPS, 4LL * sms));
+  const size_t smem = sizeof(float) * 2 * LN_WARPS * d;
+  TORCH_CHECK(smem <= 200 * 1024, "layer_norm_bwd: d too large for the shared-memory accumulators");
+  auto part_g = at::empty({grid, d}, x.options().dtype(at::kFloat));
+  auto part_b = at::empty({grid, d}, x.options().dtype(at::kFloat));
+  NT_DISPATCH_FLOAT(x.scalar_type(), "layer_norm_bwd", [&] {
+    constexpr int V = 16 / sizeof(scalar_t);
+    const bool vec = d % V == 0 && is_aligned16(x.data_ptr()) && is_aligned16(dy.data_ptr()) && is_aligned16(gamma.data_ptr());
+    auto launch = [&](auto kernel) {
+      if (smem > 48 * 1024) NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      kernel<<<grid, LN_WARPS * 32, smem, stream>>>(dy.data_ptr<scalar_t>(), x.data_ptr<scalar_t>(), gamma.data_ptr<scalar_t>(),
+          mean.data_ptr<float>(), rstd.data_ptr<float>(), dx.data_ptr<scalar_t>(), part_g.data_ptr<float>(), part_b.data_ptr<float>(), rows, d);
+    };
+    if (vec) launch(ln_bwd_kernel<scalar_t, V>); else launch(ln_bwd_kernel<scalar_t, 1>);
+  });
+  NT_KERNEL_CHECK();
+  column_sum_kernel<<<(d + 255) / 256, 256, 0, stream>>>(part_g.data_ptr<float>(), dgamma.data_ptr<float>(), grid, d);
+  NT_KERNEL_CHECK();
+  column_sum_kernel<<<(d + 255) / 256, 256, 0, stream>>>(part_b.data_ptr<float>(), dbeta.data_ptr<float>(), grid, d);
+  NT_KERNEL_CHECK();
+  return {dx, dgamma, dbeta};
+}
+
+}  // namespace nt

@@ -1,0 +1,73 @@
+// Host entry points of the extension (one declaration per kernel family).
+#pragma once
+#include <torch/extension.h>
+
+#include <string>
+#include <vector>
+
+#include "status.h"
+
+namespace nt {
+
+// ---- device status (bounded waits, checked indices)
+StatusWord* device_status_word();
+std::vector<int64_t> read_status(bool clear);  // [code, kernel, detail, count]
+
+// ---- tcgen05 GEMM (gemm_tc.cu).
+//   A: 2-D; a_mn=false -> [M, K] rows contiguous in K, a_mn=true -> [K, M] rows contiguous in M.
+//   Bs: 1..3 tensors, 2-D or [G, ., .]; b_mn=false -> [N, K], b_mn=true -> [K, N].
+//   b_split: 0 one source; 1 sources side by side along N; 2 sources stacked along K;
+//            3 two sources whose columns pair up as (gate, value) for the SwiGLU epilogue.
+//   Cs: 1..3 destinations ([M, N/len] each), or [G, M, N/len] in grouped-K mode.
+//   mode: 0 dense, 1 rows segmented by `offsets` (B[g] per segment), 2 reduction segmented (C[g]).
+//   epilogue: 0 store (+ residual `aux`, + old C when `accumulate`); 1 SwiGLU forward
+//             (C = [rows, 2N] gate|value, aux_out = H [rows, N]); 2 SwiGLU backward (aux = gate|value
+//             [rows, 2N], C = d(gate|value) [rows, 2N], the accumulator being dH).
+void gemm_tc(const at::Tensor& A, bool a_mn, const std::vector<at::Tensor>& Bs, bool b_mn, int64_t b_split,
+             const std::vector<at::Tensor>& Cs, int64_t mode, const c10::optional<at::Tensor>& offsets,
+             int64_t epilogue, bool accumulate, const c10::optional<at::Tensor>& aux,
+             const c10::optional<at::Tensor>& aux_out, int64_t force_bn);
+
+// ---- CUDA-core GEMMs (gemm_simt.cu)
+at::Tensor gemm_kernel(const at::Tensor& A, const at::Tensor& B, const std::string& implementation);
+at::Tensor tiled_gemm_kernel(const at::Tensor& A, const at::Tensor& B);
+at::Tensor naive_gemm_kernel(const at::Tensor& A, const at::Tensor& B);
+at::Tensor simt_grouped_fwd(const at::Tensor& X, const at::Tensor& off, const at::Tensor& W);
+at::Tensor simt_grouped_dx(const at::Tensor& W, const at::Tensor& off, const at::Tensor& dOut);
+at::Tensor simt_grouped_dw(const at::Tensor& X, const at::Tensor& off, const at::Tensor& dOut);
+
+// ---- grouped GEMM entry points with the reference's signatures (grouped.cu)
+at::Tensor grouped_gemm_kernel(const at::Tensor& X, const at::Tensor& offset, const at::Tensor& W);
+at::Tensor bwd_grouped_gemm_dX_kernel(const at::Tensor& W, const at::Tensor& offset, const at::Tensor& dOut);
+at::Tensor bwd_grouped_gemm_dW_kernel(const at::Tensor& X, const at::Tensor& offset, const at::Tensor& dOut);
+
+// ---- normalisation, loss, optimizer
+std::vector<at::Tensor> layer_norm_fwd(const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta, double eps);
+std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
+                                       const at::Tensor& mean, const at::Tensor& rstd);
+at::Tensor cross_entropy_fwd_bwd(at::Tensor logits, const at::Tensor& targets, int64_t V, double grad_scale, bool write_grad);
+at::Tensor adamw_step(at::Tensor param, const at::Tensor& grad, at::Tensor master, at::Tensor m, at::Tensor v, int64_t step,
+                      double lr, double beta1, double beta2, double eps, double wd, double grad_scale, bool want_sq);
+
+// ---- MoE routing / dispatch
+std::vector<at::Tensor> router_topk(const at::Tensor& x, const at::Tensor& w, int64_t k);
+std::vector<at::Tensor> assign_slots(const at::Tensor& idx, const at::Tensor& counts);
+at::Tensor count_expert_kernel(const at::Tensor& topk, const at::Tensor& mask, int64_t E, int64_t k);
+std::vector<at::Tensor> pack_fwd(const at::Tensor& x, const at::Tensor& gates, const at::Tensor& idx, const at::Tensor& slot_of);
+at::Tensor combine_fwd(const at::Tensor& y, const at::Tensor& w, const at::Tensor& rows, const c10::optional<at::Tensor>& row_start,
+                       int64_t tokens, const c10::optional<at::Tensor>& residual, bool out_f32);
+std::vector<at::Tensor> combine_bwd(const at::Tensor& y, const at::Tensor& token, const at::Tensor& w, const at::Tensor& dout);
+at::Tensor pack_bwd(const at::Tensor& dpacked, const at::Tensor& rows, const c10::optional<at::Tensor>& row_start, int64_t tokens);
+std::vector<at::Tensor> pack_tokens_kernel(const at::Tensor& X, const at::Tensor& w, const at::Tensor& e, const at::Tensor& offset_cpy);
+at::Tensor combine_tokens_kernel(const at::Tensor& Y, const at::Tensor& tokenId, const at::Tensor& w, int64_t T, int64_t d);
+std::vector<at::Tensor> combine_kernel_backward(const at::Tensor& Y, const at::Tensor& tokenId, const at::Tensor& w, const at::Tensor& dOut, int64_t d);
+std::vector<at::Tensor> pack_kernel_backward(const at::Tensor& dPackedX, const at::Tensor& dPackedW, const at::Tensor& tokenId,
+                                             const at::Tensor& expert, const at::Tensor& topk);
+
+// ---- copies and toys
+void copy_scalar(const at::Tensor& src, at::Tensor dst, int64_t n);
+void copy_vector(const at::Tensor& src, at::Tensor dst);
+void peer_copy_scalar(const at::Tensor& src, at::Tensor dst);
+at::Tensor random_op(const at::Tensor& t, int64_t x);
+
+}  // namespace nt

@@ -17,7 +17,6 @@ import torch
 import torch.nn as nn
 
 from nanotitan_b200.models.utils import ModelShardSpec, MoELayerStats
-from nanotitan_b200.ops import moe as moe_ops
 from nanotitan_b200.profiler import nvtx_range
 
 
@@ -29,27 +28,24 @@ class CUDAMoEBackend:
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None):
         batch, seq_len, d_model = x.shape
         flat = x.reshape(-1, d_model)
+        if not flat.is_cuda:
+            raise RuntimeError(f"moe_backend='cuda' needs GPU tensors (got {flat.device})")
         res = None if residual is None else residual.reshape(-1, d_model)
         if self.spec.ep_size > 1:
             from nanotitan_b200.parallel.ep import expert_parallel_moe
 
             out, counts, probs_mean = expert_parallel_moe(self, flat, res)
         else:
+            from nanotitan_b200.ops import native
+
             with nvtx_range("moe/router"):
-                gates, top_e, probs_mean, counts = moe_ops.router_topk(
-                    flat, self.router.weight, self.cfg.top_k, native=True
-                )
+                gates, top_e, probs, counts = native.router_topk(flat, self.router.weight, self.cfg.top_k)
             with nvtx_range("moe/pack_tokens"):
-                packed_x, packed_token, _, packed_gate, counts = moe_ops.pack_tokens(
-                    flat, gates, top_e, self.cfg.num_experts, native=True
-                )
-                offsets = torch.zeros(counts.numel() + 1, dtype=torch.int32, device=x.device)
-                offsets[1:] = torch.cumsum(counts, dim=0)
+                packed_x, packed_gate, packed_token, _, offsets, slot_of = native.pack(flat, gates, top_e, counts)
             with nvtx_range("moe/expert_compute"):
                 expert_out = self.experts(packed_x, offsets)
             with nvtx_range("moe/combine_tokens"):
-                out = moe_ops.combine_tokens(
-                    expert_out, packed_token, packed_gate, flat.shape[0], res, native=True
-                )
+                out = native.combine(expert_out, packed_gate, packed_token, slot_of, flat.shape[0], res)
+            probs_mean = probs.mean(dim=0)
         stats = MoELayerStats(counts.detach(), probs_per_expert=probs_mean, cfg=self.cfg)
         return out.reshape(batch, seq_len, d_model), stats

@@ -1,0 +1,124 @@
+"""AdamW on flat buckets with fp32 master weights, one fused kernel per bucket.
+
+Update rule of `torch.optim.AdamW` (the reference's optimizer, src/optim.py:6-10: weight
+decay 0.1 on every parameter, betas (0.9, 0.999), eps 1e-8).  Parameters keep their storage
+dtype (bf16 for the benchmark configs); the optimizer holds fp32 master copies and moments
+and rewrites the bf16 values after each step.  When bound to the data-parallel reducers it
+reuses their flat gradient buckets (gradients are views into them), so a step is one kernel
+per bucket with no gather or scatter of tensors.
+"""
+from __future__ import annotations
+
+import torch
+
+from nanotitan_b200.ops import reference as ref
+from nanotitan_b200.ops.ext import get_ext
+from nanotitan_b200.parallel.reducer import ReducerV1
+
+
+class _Chunk:
+    def __init__(self, bucket, params, spans):
+        self.bucket = bucket
+        self.params, self.spans = params, spans
+        n = bucket.buffer.numel()
+        flat = torch.zeros(n, dtype=bucket.dtype, device=bucket.device)
+        for p, (lo, hi) in zip(params, spans):
+            flat[lo:hi].copy_(p.data.reshape(-1))
+            p.data = flat[lo:hi].view_as(p)
+        self.flat_param = flat
+        self.master = flat.float()
+        self.exp_avg = torch.zeros_like(self.master)
+        self.exp_avg_sq = torch.zeros_like(self.master)
+
+
+class FusedAdamW(torch.optim.Optimizer):
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.1, track_grad_norm=False):
+        params = [p for p in params if p.requires_grad]
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        self._params = params
+        self._chunks: list[_Chunk] | None = None
+        self._own_reducer: ReducerV1 | None = None
+        self._step = 0
+        self.track_grad_norm = track_grad_norm
+        self._sq_parts: list[torch.Tensor] = []
+
+    # ------------------------------------------------------------------ layout
+    def bind_reducers(self, reducers: dict) -> None:
+        """Adopt the reducers' buckets as the optimizer's flat layout."""
+        assert self._chunks is None, "bind_reducers must precede the first step"
+        owned = set()
+        self._chunks = []
+        for red in reducers.values():
+            for b in red.buckets:
+                self._chunks.append(_Chunk(b, b.params, b.spans))
+                owned.update(id(p) for p in b.params)
+        rest = [p for p in self._params if id(p) not in owned]
+        if rest:
+            self._own_reducer = ReducerV1(rest, 1, None, bucket_size=1 << 20)
+            for b in self._own_reducer.buckets:
+                self._chunks.append(_Chunk(b, b.params, b.spans))
+
+    def _ensure_layout(self) -> None:
+        if self._chunks is None:
+            self.bind_reducers({})
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        self._ensure_layout()
+        for c in self._chunks:
+            c.bucket.buffer.zero_()
+
+    # ------------------------------------------------------------------ step
+    @torch.no_grad()
+    def step(self, closure=None):
+        self._ensure_layout()
+        self._step += 1
+        group = self.param_groups[0]
+        beta1, beta2 = group["betas"]
+        self._sq_parts = []
+        for c in self._chunks:
+            grads = c.bucket.buffer
+            for p, (lo, hi) in zip(c.params, c.spans):  # a gradient that is not the bucket view
+                if p.grad is not None and p.grad.data_ptr() != grads[lo:hi].data_ptr():
+                    grads[lo:hi].copy_(p.grad.reshape(-1))
+                    p.grad = grads[lo:hi].view_as(p)
+            if grads.is_cuda:
+                part = get_ext().adamw_step(c.flat_param, grads, c.master, c.exp_avg, c.exp_avg_sq, self._step,
+                                            group["lr"], beta1, beta2, group["eps"], group["weight_decay"], 1.0,
+                                            self.track_grad_norm)
+                if self.track_grad_norm:
+                    self._sq_parts.append(part.sum())
+            else:
+                ref.adamw_step(c.master, grads.float(), c.exp_avg, c.exp_avg_sq, self._step, group["lr"], beta1, beta2,
+                               group["eps"], group["weight_decay"])
+                c.flat_param.copy_(c.master)
+        return None
+
+    def last_grad_norm(self) -> float:
+        if not self._sq_parts:
+            return 0.0
+        return float(torch.stack(self._sq_parts).sum().sqrt().item())
+
+    # ------------------------------------------------------------------ checkpoints
+    def state_dict(self):
+        self._ensure_layout()
+        per_param = []
+        for c in self._chunks:
+            for lo, hi in c.spans:
+                per_param.append({"master": c.master[lo:hi].clone().cpu(), "exp_avg": c.exp_avg[lo:hi].clone().cpu(),
+                                  "exp_avg_sq": c.exp_avg_sq[lo:hi].clone().cpu()})
+        return {"step": self._step, "per_param": per_param,
+                "hyper": {k: v for k, v in self.param_groups[0].items() if k != "params"}}
+
+    def load_state_dict(self, state):
+        self._ensure_layout()
+        self._step = state["step"]
+        it = iter(state["per_param"])
+        for c in self._chunks:
+            for lo, hi in c.spans:
+                rec = next(it)
+                c.master[lo:hi].copy_(rec["master"])
+                c.exp_avg[lo:hi].copy_(rec["exp_avg"])
+                c.exp_avg_sq[lo:hi].copy_(rec["exp_avg_sq"])
+            c.flat_param.copy_(c.master)
+        for k, v in state.get("hyper", {}).items():
+            self.param_groups[0][k] = v

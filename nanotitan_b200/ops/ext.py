@@ -54,10 +54,9 @@ def build_extension(verbose: bool = False) -> Path:
         extra_include_paths=[str(CSRC), str(CSRC / "runtime")],
         extra_cflags=["-O3", "-std=c++17"],
         extra_cuda_cflags=NVCC_FLAGS,
-        extra_ldflags=["-lcuda"],
         build_directory=str(BUILD_DIR),
         verbose=verbose,
-        is_python_module=False,
+        is_python_module=True,
     )
     path = so_path()
     if path is None:

@@ -1,0 +1,38 @@
+"""tcgen05 flash-attention kernels (forward and backward) behind an autograd Function."""
+from __future__ import annotations
+
+import torch
+
+from nanotitan_b200.ops.ext import get_ext
+
+
+def supported(q, k, v) -> bool:
+    ext = get_ext()
+    if not hasattr(ext, "flash_fwd"):
+        return False
+    return (
+        q.dtype in (torch.bfloat16, torch.float16)
+        and q.shape[-1] in (32, 64, 128)
+        and q.shape == k.shape == v.shape
+    )
+
+
+class _Flash(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale):
+        ext = get_ext()
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        out, lse = ext.flash_fwd(q, k, v, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.scale = scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = get_ext().flash_bwd(dout.contiguous(), q, k, v, out, lse, ctx.scale)
+        return dq, dk, dv, None
+
+
+def flash_attention(q, k, v, scale):
+    return _Flash.apply(q, k, v, scale)

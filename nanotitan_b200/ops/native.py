@@ -1,0 +1,339 @@
+"""Autograd Functions over the `nanotitan_cuda` kernels (GPU tensors only).
+
+GEMM-shaped work goes to the tcgen05 kernel (`gemm_tc`) whenever its operands are
+bf16/fp16 with 16-byte aligned rows; operands it cannot take (fp32, odd widths) go to
+cuBLAS through torch, which only happens off the benchmarked path.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from nanotitan_b200.ops.ext import get_ext
+
+DENSE, GROUPED_M, GROUPED_K = 0, 1, 2
+B_ONE, B_SPLIT_N, B_SPLIT_K, B_DUAL = 0, 1, 2, 3
+EPI_STORE, EPI_SWIGLU_FWD, EPI_SWIGLU_BWD = 0, 1, 2
+
+
+def tc_ok(*tensors: torch.Tensor) -> bool:
+    """True when every tensor can be a TMA operand of the tcgen05 GEMM."""
+    for t in tensors:
+        if t.dtype not in (torch.bfloat16, torch.float16) or not t.is_cuda:
+            return False
+        if t.stride(-1) != 1 or t.size(-1) % 8 or t.stride(-2) % 8 or t.data_ptr() % 16:
+            return False
+        if t.dim() == 3 and t.stride(0) % 8:
+            return False
+    return True
+
+
+def gemm_tc(a, a_mn, bs, b_mn, cs, *, b_split=B_ONE, mode=DENSE, offsets=None, epilogue=EPI_STORE,
+            accumulate=False, aux=None, aux_out=None, force_bn=0):
+    get_ext().gemm_tc(a, a_mn, list(bs), b_mn, b_split, list(cs), mode, offsets, epilogue, accumulate,
+                      aux, aux_out, force_bn)
+
+
+def _rows(t: torch.Tensor) -> torch.Tensor:
+    """2-D row-major view/copy of the leading dims."""
+    t2 = t.reshape(-1, t.shape[-1])
+    return t2 if t2.stride(-1) == 1 and t2.stride(0) % 8 == 0 else t2.contiguous()
+
+
+# ------------------------------------------------------------------------------- linear
+class _Linear(torch.autograd.Function):
+    """y = x @ w (+ residual), w stored [in, out]."""
+
+    @staticmethod
+    def forward(ctx, x, w, residual):
+        x2 = _rows(x)
+        y = torch.empty(x2.shape[0], w.shape[1], dtype=x.dtype, device=x.device)
+        res = None if residual is None else _rows(residual)
+        gemm_tc(x2, False, [w], True, [y], aux=res)
+        ctx.save_for_backward(x2, w)
+        ctx.has_res = residual is not None
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = _rows(dy)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x2)
+            gemm_tc(dy2, False, [w], False, [dx])  # w as [N_out = in, K = out]: K-major
+            dx = dx.view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            dw = torch.empty_like(w)
+            gemm_tc(x2, True, [dy2], True, [dw])  # x^T dy: both operands MN-major
+        return dx, dw, (dy if ctx.has_res else None)
+
+
+def linear(x, w, residual=None):
+    if tc_ok(x.reshape(-1, x.shape[-1]), w) and w.dim() == 2:
+        return _Linear.apply(x, w, residual)
+    y = x @ w
+    return y if residual is None else y + residual
+
+
+# ------------------------------------------------------------------------------- layer norm
+class _LayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps):
+        xc = x.contiguous()
+        y, mean, rstd = get_ext().layer_norm_fwd(xc, gamma.contiguous(), beta.contiguous(), eps)
+        ctx.save_for_backward(xc, gamma, mean, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, gamma, mean, rstd = ctx.saved_tensors
+        dx, dgamma, dbeta = get_ext().layer_norm_bwd(dy.contiguous(), x, gamma.contiguous(), mean, rstd)
+        return dx, dgamma.to(gamma.dtype), dbeta.to(gamma.dtype), None
+
+
+def layer_norm(x, gamma, beta, eps=1e-8):
+    if gamma.dtype != x.dtype:
+        gamma, beta = gamma.to(x.dtype), beta.to(x.dtype)
+    return _LayerNorm.apply(x, gamma, beta, eps)
+
+
+# ------------------------------------------------------------------------------- attention
+def causal_attention(q, k, v, scale=None):
+    """[B, S, H, Dh] causal attention on the tcgen05 flash kernels."""
+    from nanotitan_b200.ops import attention
+
+    return attention.causal_attention(q, k, v, scale)
+
+
+# ------------------------------------------------------------------------------- loss
+class _CrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets):
+        rows = logits.reshape(-1, logits.shape[-1])
+        work = rows.clone() if rows.stride(-1) == 1 else rows.contiguous()
+        n = max(int(work.shape[0]), 1)
+        row_loss = get_ext().cross_entropy_fwd_bwd(work, targets.reshape(-1).contiguous(), work.shape[1], 1.0 / n, True)
+        ctx.save_for_backward(work)
+        ctx.shape = logits.shape
+        return row_loss.sum() / n
+
+    @staticmethod
+    def backward(ctx, g):
+        (dlogits,) = ctx.saved_tensors
+        return (dlogits * g.to(dlogits.dtype)).view(ctx.shape), None
+
+
+def cross_entropy(logits, targets):
+    return _CrossEntropy.apply(logits, targets)
+
+
+class _LinearCrossEntropy(torch.autograd.Function):
+    """mean CE(x @ w^T, targets) with w [V, d].  The bf16 logits live in one padded buffer that
+    the loss kernel overwrites with their gradient; dx and dw are formed at once, so backward
+    only scales them."""
+
+    @staticmethod
+    def forward(ctx, x, w, targets):
+        ext = get_ext()
+        rows, vocab = x.shape[0], w.shape[0]
+        ld = (vocab + 63) // 64 * 64
+        logits = torch.empty(rows, ld, dtype=x.dtype, device=x.device)
+        view = logits[:, :vocab]
+        gemm_tc(x, False, [w], False, [view])  # w [V, d]: K-major B
+        row_loss = ext.cross_entropy_fwd_bwd(logits, targets.contiguous(), vocab, 1.0 / max(rows, 1), True)
+        loss = row_loss.sum() / max(rows, 1)
+        dx = torch.empty_like(x)
+        gemm_tc(view, False, [w], True, [dx])  # reduction over V: w [V, d] is MN-major here
+        dw = torch.empty_like(w)
+        gemm_tc(view, True, [x], True, [dw])  # dlogits^T x
+        ctx.save_for_backward(dx, dw)
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        dx, dw = ctx.saved_tensors
+        return dx * g.to(dx.dtype), dw * g.to(dw.dtype), None
+
+
+def linear_cross_entropy(x, w_unembed, targets):
+    x2 = _rows(x)
+    if tc_ok(x2, w_unembed):
+        return _LinearCrossEntropy.apply(x2, w_unembed, targets.reshape(-1))
+    return cross_entropy(x2 @ w_unembed.t(), targets.reshape(-1))
+
+
+# ------------------------------------------------------------------------------- MoE routing
+class _Router(torch.autograd.Function):
+    """Fused fp32 router.  Outputs: gates [T,k] (grad -> x and w), ids [T,k], probs [T,E]
+    (grad -> w only: the load-balancing loss sees detached tokens), counts [E]."""
+
+    @staticmethod
+    def forward(ctx, x, w, k):
+        gates, idx, probs, counts = get_ext().router_topk(x.contiguous(), w.contiguous(), k)
+        ctx.save_for_backward(x, w, gates, idx, probs)
+        ctx.mark_non_differentiable(idx, counts)
+        return gates, idx, probs, counts
+
+    @staticmethod
+    def backward(ctx, dgates, _didx, dprobs, _dcounts):
+        x, w, gates, idx, probs = ctx.saved_tensors
+        idx64 = idx.long()
+        top_sum = probs.gather(1, idx64).sum(dim=1, keepdim=True)
+        dp_top = (dgates - (dgates * gates).sum(dim=1, keepdim=True)) / top_sum
+        dp = torch.zeros_like(probs).scatter_(1, idx64, dp_top)
+        dl_tokens = probs * (dp - (dp * probs).sum(dim=1, keepdim=True))  # reaches x and w
+        dl_all = dl_tokens
+        if dprobs is not None:
+            dl_all = dl_tokens + probs * (dprobs - (dprobs * probs).sum(dim=1, keepdim=True))
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = dl_tokens.to(x.dtype) @ w.to(x.dtype)
+        if ctx.needs_input_grad[1]:
+            dw = (dl_all.to(x.dtype).t() @ x).to(w.dtype)
+        return dx, dw, None
+
+
+def router_topk(x, w, k):
+    return _Router.apply(x, w, k)
+
+
+# ------------------------------------------------------------------------------- pack / combine
+class _Pack(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gates, idx, counts):
+        ext = get_ext()
+        offsets, slot_of = ext.assign_slots(idx, counts)
+        px, ptok, pexp, pgate = ext.pack_fwd(x.contiguous(), gates.contiguous(), idx, slot_of)
+        ctx.save_for_backward(slot_of)
+        ctx.tokens = x.shape[0]
+        ctx.mark_non_differentiable(ptok, pexp, offsets, slot_of)
+        return px, pgate, ptok, pexp, offsets, slot_of
+
+    @staticmethod
+    def backward(ctx, dpx, dpgate, *_):
+        (slot_of,) = ctx.saved_tensors
+        dx = get_ext().pack_bwd(dpx.contiguous(), slot_of.view(-1), None, ctx.tokens) if dpx is not None else None
+        dgates = dpgate[slot_of.long()] if dpgate is not None else None
+        return dx, dgates, None, None
+
+
+def pack(x, gates, idx, counts):
+    """-> packed_x, packed_gate, packed_token, packed_expert, offsets [E+1], slot_of [T,k]."""
+    return _Pack.apply(x, gates, idx, counts)
+
+
+def pack_tokens(x, gates, top_e, num_experts):
+    idx = top_e.to(torch.int32).contiguous()
+    counts = get_ext().count_expert_kernel(idx, idx.new_empty(0), num_experts, idx.shape[1])
+    px, pgate, ptok, pexp, _, _ = pack(x, gates.float(), idx, counts)
+    return px, ptok, pexp, pgate, counts
+
+
+class _Combine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, gate, rows, row_start, token, num_tokens, residual):
+        yc = y.contiguous()
+        res = None if residual is None else residual.contiguous()
+        out = get_ext().combine_fwd(yc, gate.contiguous(), rows, row_start, num_tokens, res, False)
+        ctx.save_for_backward(yc, gate, token)
+        ctx.has_res = residual is not None
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        y, gate, token = ctx.saved_tensors
+        dy, dgate = get_ext().combine_bwd(y, token, gate.contiguous(), dout.contiguous())
+        return dy, dgate, None, None, None, None, (dout if ctx.has_res else None)
+
+
+def combine(y, packed_gate, packed_token, slot_of, num_tokens, residual=None):
+    """Fixed fan-out combine: token t owns packed rows slot_of[t, :]."""
+    return _Combine.apply(y, packed_gate, slot_of.view(-1), None, packed_token, num_tokens, residual)
+
+
+def _csr(token: torch.Tensor, num_tokens: int):
+    tok = token.long()
+    order = torch.sort(tok, stable=True).indices.to(torch.int32)
+    start = torch.zeros(num_tokens + 1, dtype=torch.int32, device=token.device)
+    start[1:] = torch.cumsum(torch.bincount(tok, minlength=num_tokens), 0)
+    return start, order
+
+
+def combine_tokens(y, packed_token, packed_gate, num_tokens, residual=None, slot_of=None):
+    tok = packed_token.to(torch.int32).contiguous()
+    if slot_of is not None:
+        return combine(y, packed_gate, tok, slot_of, num_tokens, residual)
+    start, order = _csr(tok, num_tokens)
+    return _Combine.apply(y, packed_gate.float(), order, start, tok, num_tokens, residual)
+
+
+# ------------------------------------------------------------------------------- expert GEMMs
+class _GroupedGemm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, offsets, w):
+        ctx.save_for_backward(x, offsets, w)
+        return get_ext().grouped_gemm_kernel(x, offsets, w)
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, offsets, w = ctx.saved_tensors
+        ext = get_ext()
+        dout = dout.contiguous()
+        dx = ext.bwd_grouped_gemm_dX_kernel(w, offsets, dout) if ctx.needs_input_grad[0] else None
+        dw = ext.bwd_grouped_gemm_dW_kernel(x, offsets, dout) if ctx.needs_input_grad[2] else None
+        return dx, None, dw
+
+
+def grouped_gemm(x, w, offsets):
+    return _GroupedGemm.apply(x, offsets, w)
+
+
+class _SwigluExperts(torch.autograd.Function):
+    """Three grouped tcgen05 GEMMs forward (gate|value with the SwiGLU in the epilogue, then the
+    down projection), four backward (dH with the SwiGLU derivative in the epilogue, dX over the
+    stacked gate|value reduction, and the two weight-gradient GEMMs over ragged segments)."""
+
+    @staticmethod
+    def forward(ctx, x, w_gate, w_val, w_out, offsets):
+        rows, f, d = x.shape[0], w_gate.shape[2], w_out.shape[2]
+        gv = torch.empty(rows, 2 * f, dtype=x.dtype, device=x.device)
+        h = torch.empty(rows, f, dtype=x.dtype, device=x.device)
+        gemm_tc(x, False, [w_gate, w_val], True, [gv], b_split=B_DUAL, mode=GROUPED_M, offsets=offsets,
+                epilogue=EPI_SWIGLU_FWD, aux_out=h)
+        y = torch.empty(rows, d, dtype=x.dtype, device=x.device)
+        gemm_tc(h, False, [w_out], True, [y], mode=GROUPED_M, offsets=offsets)
+        ctx.save_for_backward(x, w_gate, w_val, w_out, offsets, gv, h)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w_gate, w_val, w_out, offsets, gv, h = ctx.saved_tensors
+        dy = dy.contiguous()
+        dgv = torch.empty_like(gv)
+        gemm_tc(dy, False, [w_out], False, [dgv], mode=GROUPED_M, offsets=offsets, epilogue=EPI_SWIGLU_BWD, aux=gv)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            gemm_tc(dgv, False, [w_gate, w_val], False, [dx], b_split=B_SPLIT_K, mode=GROUPED_M, offsets=offsets)
+        d_out = torch.empty_like(w_out)
+        gemm_tc(h, True, [dy], True, [d_out], mode=GROUPED_K, offsets=offsets)
+        d_gate, d_val = torch.empty_like(w_gate), torch.empty_like(w_val)
+        gemm_tc(x, True, [dgv], True, [d_gate, d_val], mode=GROUPED_K, offsets=offsets)
+        return dx, d_gate, d_val, d_out, None
+
+
+def swiglu_experts(x, w_gate, w_val, w_out, offsets):
+    offsets = offsets.to(torch.int32)
+    f = w_gate.shape[2]
+    if tc_ok(x, w_gate, w_val, w_out) and f % 64 == 0 and w_gate.shape[0] <= 256:
+        return _SwigluExperts.apply(x.contiguous(), w_gate, w_val, w_out, offsets.contiguous())
+    gate = grouped_gemm(x, w_gate, offsets)
+    val = grouped_gemm(x, w_val, offsets)
+    return grouped_gemm(torch.nn.functional.silu(gate) * val, w_out, offsets)
+
+
+def default_scale(d_head: int) -> float:
+    return 1.0 / math.sqrt(d_head)

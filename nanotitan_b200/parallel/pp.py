@@ -100,7 +100,9 @@ class PipelineParallel:
                     p.grad = None
 
     # ------------------------------------------------------------------ step
-    def train_step(self, model, batch, optimizer):
+    def train_step(self, model, batch, optimizer, collect_metrics: bool = True):
+        """One optimizer step.  `collect_metrics=False` skips the host read of the losses and the
+        end-of-step device sync (the step is still complete on the stream) and returns None."""
         x, y = batch
         n_mb = self.cfg.runtime.num_microbatches
         microbatch_x, microbatch_y = self.prepare_microbatch(x, y)
@@ -162,6 +164,8 @@ class PipelineParallel:
         for _, work in self._pending:
             work.wait()
         self._pending = []
+        if not collect_metrics:
+            return None
 
         # One host read for all loss values (also the step's only device sync).
         if last:
