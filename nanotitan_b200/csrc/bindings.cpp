@@ -31,6 +31,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("Cs"), py::arg("mode") = 0, py::arg("offsets") = py::none(), py::arg("epilogue") = 0,
         py::arg("accumulate") = false, py::arg("aux") = py::none(), py::arg("aux_out") = py::none(),
         py::arg("force_bn") = 0);
+  m.def("flash_fwd", &nt::flash_fwd, "Causal flash attention forward -> (out, lse)");
+  m.def("flash_bwd", &nt::flash_bwd, "Causal flash attention backward -> (dq, dk, dv)");
   m.def("layer_norm_fwd", &nt::layer_norm_fwd);
   m.def("layer_norm_bwd", &nt::layer_norm_bwd);
   m.def("cross_entropy_fwd_bwd", &nt::cross_entropy_fwd_bwd);

@@ -49,6 +49,11 @@ at::Tensor cross_entropy_fwd_bwd(at::Tensor logits, const at::Tensor& targets, i
 at::Tensor adamw_step(at::Tensor param, const at::Tensor& grad, at::Tensor master, at::Tensor m, at::Tensor v, int64_t step,
                       double lr, double beta1, double beta2, double eps, double wd, double grad_scale, bool want_sq);
 
+// ---- flash attention (flash_attn.cu): [B, S, H, Dh] tensors, Dh in {32, 64}
+std::vector<at::Tensor> flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale);
+std::vector<at::Tensor> flash_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                  const at::Tensor& out, const at::Tensor& lse, double scale);
+
 // ---- MoE routing / dispatch
 std::vector<at::Tensor> router_topk(const at::Tensor& x, const at::Tensor& w, int64_t k);
 std::vector<at::Tensor> assign_slots(const at::Tensor& idx, const at::Tensor& counts);

@@ -22,6 +22,9 @@ from nanotitan_b200.profiler import nvtx_range
 class TorchMoEBackend:
     def __init__(self, cfg, experts: nn.Module, router: nn.Linear, spec: ModelShardSpec):
         self.cfg, self.spec, self.router, self.experts = cfg, spec, router, experts
+        # False: the load-balancing loss back-propagates into the tokens (the reference's torch
+        # backend).  True: it sees detached tokens, as the CUDA backends do.
+        self.aux_on_detached_tokens = False
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None):
         batch, seq_len, d_model = x.shape
@@ -62,5 +65,7 @@ class TorchMoEBackend:
         if residual is not None:
             out = out + residual.reshape(-1, d_model)
 
+        if self.aux_on_detached_tokens:
+            probs = ref.router_topk(flat.detach(), self.router.weight, self.cfg.top_k)[2]
         stats = MoELayerStats(counts.detach(), probs_per_expert=probs, cfg=self.cfg)
         return out.reshape(batch, seq_len, d_model), stats

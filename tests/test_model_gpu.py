@@ -23,6 +23,9 @@ def _oracle(model, cfg):
     with torch.no_grad():
         for (k, v), (_, ov) in zip(model.state_dict().items(), oracle.state_dict().items()):
             ov.copy_(v.float())
+    for block in oracle.blocks:
+        if hasattr(block, "ffn"):
+            block.ffn.moe_backend.aux_on_detached_tokens = True  # the semantics of the CUDA backend
     return oracle
 
 
@@ -43,12 +46,13 @@ def test_forward_loss_and_gradients_match_fp32_oracle(experts, top_k, monkeypatc
     (want + oaux).backward()
     assert abs(loss.item() - want.item()) < 3e-2 * max(1.0, abs(want.item()))
     assert sum(s.tokens_per_expert.sum().item() for s in stats) == cfg.n_layers * x.numel() * top_k
-    worst = 0.0
+    errors = {}
     for (name, p), (_, q) in zip(model.named_parameters(), oracle.named_parameters()):
         assert p.grad is not None, name
         denom = q.grad.abs().max().item() + 1e-6
-        worst = max(worst, (p.grad.float() - q.grad).abs().max().item() / denom)
-    assert worst < 0.12, f"worst relative gradient error {worst}"
+        errors[name] = (p.grad.float() - q.grad).abs().max().item() / denom
+    bad = {k: round(v, 3) for k, v in errors.items() if v >= 0.12}
+    assert not bad, f"relative gradient errors: {bad}"
 
 
 def test_training_reduces_loss_and_uses_native_kernels():
