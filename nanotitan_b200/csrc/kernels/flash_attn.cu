@@ -524,16 +524,28 @@ std::vector<at::Tensor> flash_fwd(const at::Tensor& q, const at::Tensor& k, cons
 }
 
 // -> (dq, dk, dv), each [B, S, H, Dh]
+// `grads`: empty, or three preallocated [B, S, H, Dh] views with identical strides (e.g. the
+// thirds of one fused dQKV buffer) that receive dq, dk, dv.
 std::vector<at::Tensor> flash_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
-                                  const at::Tensor& out, const at::Tensor& lse, double scale) {
+                                  const at::Tensor& out, const at::Tensor& lse, double scale, const std::vector<at::Tensor>& grads) {
   using namespace flash;
   check_bshd(q, "q"); check_bshd(k, "k"); check_bshd(v, "v"); check_bshd(dout, "dout"); check_bshd(out, "out");
   TORCH_CHECK(dout.is_contiguous() && out.is_contiguous(), "dout and out must be contiguous");
   c10::cuda::CUDAGuard guard(q.device());
   const int B = q.size(0), S = q.size(1), H = q.size(2), DH = q.size(3);
-  auto dq = at::empty({B, S, H, DH}, q.options());
-  auto dk = at::empty({B, S, H, DH}, q.options());
-  auto dv = at::empty({B, S, H, DH}, q.options());
+  at::Tensor dq, dk, dv;
+  if (grads.size() == 3) {
+    dq = grads[0]; dk = grads[1]; dv = grads[2];
+    for (const auto& g : grads)
+      TORCH_CHECK(g.sizes() == q.sizes() && g.strides() == dq.strides() && g.stride(3) == 1 && g.scalar_type() == q.scalar_type() &&
+                      g.stride(2) % 8 == 0 && g.stride(1) % 8 == 0 && reinterpret_cast<uintptr_t>(g.data_ptr()) % 16 == 0,
+                  "flash_bwd: gradient outputs must be same-strided, 16-byte aligned [B, S, H, Dh] views");
+  } else {
+    TORCH_CHECK(grads.empty(), "flash_bwd: pass zero or three gradient outputs");
+    dq = at::empty({B, S, H, DH}, q.options());
+    dk = at::empty({B, S, H, DH}, q.options());
+    dv = at::empty({B, S, H, DH}, q.options());
+  }
   if (q.numel() == 0) return {dq, dk, dv};
   auto dsum = at::empty({B, H, S}, lse.options());
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();

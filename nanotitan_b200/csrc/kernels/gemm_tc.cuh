@@ -49,10 +49,15 @@ struct Args {
   long long ldr;
   void* C2;  // kEpiSwigluFwd: H output
   long long ldc2;
+  // grouped-K only: every segment's reduction is cut into `k_splits` parts whose fp32 partial
+  // tiles go to `ws` ([k_splits][G][M][N]); a second kernel folds them in a fixed order.
+  int k_splits;
+  float* ws;
   StatusWord* status;
 };
 
 struct Tile {
+  int split;       // grouped-K: which part of the segment's reduction
   int g;           // group
   int m0;          // first row of the tile: A/C row (dense, grouped-M) or C[g] row (grouped-K)
   int rows_valid;  // rows of the tile that exist
@@ -86,7 +91,7 @@ __device__ __forceinline__ int total_tiles(const Args& a, const int* tile_start)
   const int n_tiles = ceil_div(a.N, tile_n<BN, EPI>());
   if (a.mode == kDense) return ceil_div(a.M, BM) * n_tiles;
   if (a.mode == kGroupedM) return tile_start[a.G] * n_tiles;
-  return a.G * ceil_div(a.M, BM) * n_tiles;
+  return a.k_splits * a.G * ceil_div(a.M, BM) * n_tiles;
 }
 
 template <int BN, int EPI>
@@ -99,6 +104,7 @@ __device__ __forceinline__ Tile get_tile(const Args& a, const int* tile_start, i
   ti.n0 = nt * tn;
   ti.k_row0 = 0;
   ti.k_rows = 0;
+  ti.split = 0;
   if (a.mode == kDense) {
     ti.g = 0;
     ti.m0 = mt * BM;
@@ -114,12 +120,19 @@ __device__ __forceinline__ Tile get_tile(const Args& a, const int* tile_start, i
     ti.k_chunks = ceil_div(a.K, BK);
   } else {
     const int m_tiles = ceil_div(a.M, BM);
-    ti.g = mt / m_tiles;
+    const int sg = mt / m_tiles;  // split-major, then group
+    ti.split = sg / a.G;
+    ti.g = sg - ti.split * a.G;
     ti.m0 = (mt % m_tiles) * BM;
     ti.rows_valid = min(BM, a.M - ti.m0);
-    ti.k_row0 = a.offsets[ti.g];
-    ti.k_rows = a.offsets[ti.g + 1] - ti.k_row0;
-    ti.k_chunks = ceil_div(ti.k_rows, BK);
+    const int seg0 = a.offsets[ti.g];
+    const int seg_rows = a.offsets[ti.g + 1] - seg0;
+    const int chunks_total = ceil_div(seg_rows, BK);
+    const int per_split = ceil_div(chunks_total, a.k_splits);
+    const int chunk0 = ti.split * per_split;
+    ti.k_chunks = max(0, min(per_split, chunks_total - chunk0));
+    ti.k_row0 = seg0 + chunk0 * BK;
+    ti.k_rows = max(0, seg_rows - chunk0 * BK);  // rows from this part's start to the segment's end
   }
   return ti;
 }
@@ -404,6 +417,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
       if constexpr (EPI == kEpiStore) {
         const long long grp_off = (args.mode == kGroupedK) ? static_cast<long long>(ti.g) * args.c_group_stride : 0;
+        const bool partial = args.mode == kGroupedK && args.k_splits > 1;
+        float* ws_tile = partial ? args.ws + (static_cast<long long>(ti.split) * args.G + ti.g) * args.M * args.N : nullptr;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           const int col = ti.n0 + c0;
@@ -419,7 +434,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0.f;
           }
-          if (row_ok) {
+          if (row_ok && partial) {
+            store_row32(ws_tile, row * args.N + col, min(32, args.N - col), args.dtype, true, v);
+          } else if (row_ok) {
             const int valid = min(32, args.N - col);
             if (args.R != nullptr) {
               float rr[32];

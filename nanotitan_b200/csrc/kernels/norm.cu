@@ -118,13 +118,100 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __rest
   }
 }
 
-// out[c] = sum over `parts` rows of in[p][c], rows visited in index order.
+// Register-resident variant for d <= CHUNKS * 32 * VEC: lane l owns columns (j*32 + l)*VEC.. of
+// every row its warp visits, so dgamma/dbeta partial sums never leave registers until the end
+// and each row is read from memory once.
+template <typename T, int VEC, int CHUNKS>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+ln_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
+                  const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx,
+                  float* __restrict__ part_gamma, float* __restrict__ part_beta, long long rows, int d) {
+  extern __shared__ float acc[];  // [2][LN_WARPS][d], used once at the end
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float gv[CHUNKS][VEC], ag[CHUNKS][VEC], ab[CHUNKS][VEC];
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) {
+    const int c = (j * 32 + lane) * VEC;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) { ag[j][i] = 0.f; ab[j][i] = 0.f; gv[j][i] = 0.f; }
+    if (c < d) load_vec<T, VEC>(gamma + c, gv[j]);
+  }
+  for (long long row = static_cast<long long>(blockIdx.x) * LN_WARPS + warp; row < rows;
+       row += static_cast<long long>(gridDim.x) * LN_WARPS) {
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    float xh[CHUNKS][VEC], dv[CHUNKS][VEC];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+      const int c = (j * 32 + lane) * VEC;
+      if (c < d) {
+        load_vec<T, VEC>(x + row * d + c, xh[j]);
+        load_vec<T, VEC>(dy + row * d + c, dv[j]);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          xh[j][i] = (xh[j][i] - mean) * rstd;
+          const float gy = gv[j][i] * dv[j][i];
+          s1 += gy;
+          s2 += gy * xh[j][i];
+          ag[j][i] += dv[j][i] * xh[j][i];
+          ab[j][i] += dv[j][i];
+        }
+      }
+    }
+    s1 = warp_sum(s1) / d;
+    s2 = warp_sum(s2) / d;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+      const int c = (j * 32 + lane) * VEC;
+      if (c < d) {
+        float out[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) out[i] = rstd * (gv[j][i] * dv[j][i] - s1 - xh[j][i] * s2);
+        store_vec<T, VEC>(dx + row * d + c, out);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) {
+    const int c = (j * 32 + lane) * VEC;
+    if (c < d) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        acc[warp * d + c + i] = ag[j][i];
+        acc[(LN_WARPS + warp) * d + c + i] = ab[j][i];
+      }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float g = 0.f, b = 0.f;
+#pragma unroll
+    for (int w = 0; w < LN_WARPS; ++w) {
+      g += acc[w * d + c];
+      b += acc[(LN_WARPS + w) * d + c];
+    }
+    part_gamma[static_cast<long long>(blockIdx.x) * d + c] = g;
+    part_beta[static_cast<long long>(blockIdx.x) * d + c] = b;
+  }
+}
+
+// out[c] = sum over `parts` rows of in[p][c].  Block = 32 columns x 8 row groups; each group adds
+// its rows in index order and the 8 group sums are added in group order, so the result does not
+// depend on scheduling.
 __global__ void column_sum_kernel(const float* __restrict__ in, float* __restrict__ out, int parts, int d) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= d) return;
+  __shared__ float red[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int p = 0; p < parts; ++p) s += in[static_cast<long long>(p) * d + c];
-  out[c] = s;
+  if (c < d)
+    for (int p = threadIdx.y; p < parts; p += 8) s += in[static_cast<long long>(p) * d + c];
+  red[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < d) {
+    float t = 0.f;
+#pragma unroll
+    for (int y = 0; y < 8; ++y) t += red[y][threadIdx.x];
+    out[c] = t;
+  }
 }
 
 }  // namespace
@@ -181,12 +268,16 @@ std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x
       kernel<<<grid, LN_WARPS * 32, smem, stream>>>(dy.data_ptr<scalar_t>(), x.data_ptr<scalar_t>(), gamma.data_ptr<scalar_t>(),
           mean.data_ptr<float>(), rstd.data_ptr<float>(), dx.data_ptr<scalar_t>(), part_g.data_ptr<float>(), part_b.data_ptr<float>(), rows, d);
     };
-    if (vec) launch(ln_bwd_kernel<scalar_t, V>); else launch(ln_bwd_kernel<scalar_t, 1>);
+    if (vec && d <= 32 * V) launch(ln_bwd_reg_kernel<scalar_t, V, 1>);
+    else if (vec && d <= 64 * V) launch(ln_bwd_reg_kernel<scalar_t, V, 2>);
+    else if (vec && d <= 128 * V) launch(ln_bwd_reg_kernel<scalar_t, V, 4>);
+    else if (vec) launch(ln_bwd_kernel<scalar_t, V>);
+    else launch(ln_bwd_kernel<scalar_t, 1>);
   });
   NT_KERNEL_CHECK();
-  column_sum_kernel<<<(d + 255) / 256, 256, 0, stream>>>(part_g.data_ptr<float>(), dgamma.data_ptr<float>(), grid, d);
+  column_sum_kernel<<<(d + 31) / 32, dim3(32, 8), 0, stream>>>(part_g.data_ptr<float>(), dgamma.data_ptr<float>(), grid, d);
   NT_KERNEL_CHECK();
-  column_sum_kernel<<<(d + 255) / 256, 256, 0, stream>>>(part_b.data_ptr<float>(), dbeta.data_ptr<float>(), grid, d);
+  column_sum_kernel<<<(d + 31) / 32, dim3(32, 8), 0, stream>>>(part_b.data_ptr<float>(), dbeta.data_ptr<float>(), grid, d);
   NT_KERNEL_CHECK();
   return {dx, dgamma, dbeta};
 }

@@ -52,7 +52,7 @@ at::Tensor adamw_step(at::Tensor param, const at::Tensor& grad, at::Tensor maste
 // ---- flash attention (flash_attn.cu): [B, S, H, Dh] tensors, Dh in {32, 64}
 std::vector<at::Tensor> flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale);
 std::vector<at::Tensor> flash_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
-                                  const at::Tensor& out, const at::Tensor& lse, double scale);
+                                  const at::Tensor& out, const at::Tensor& lse, double scale, const std::vector<at::Tensor>& grads);
 
 // ---- MoE routing / dispatch
 std::vector<at::Tensor> router_topk(const at::Tensor& x, const at::Tensor& w, int64_t k);

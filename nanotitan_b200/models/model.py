@@ -130,11 +130,7 @@ class MultiHeadAttention(nn.Module):
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         batch, seq, d_model = x.shape
         heads, d_head = self.cfg.n_heads, self.cfg.d_head
-        flat = x.reshape(-1, d_model)
-        q = ops.linear(flat, self.W_Q).view(batch, seq, heads, d_head)
-        k = ops.linear(flat, self.W_K).view(batch, seq, heads, d_head)
-        v = ops.linear(flat, self.W_V).view(batch, seq, heads, d_head)
-        ctx = ops.causal_attention(q, k, v, 1.0 / math.sqrt(d_head))
+        ctx = ops.qkv_attention(x, self.W_Q, self.W_K, self.W_V, heads, d_head, 1.0 / math.sqrt(d_head))
         res = None if residual is None else residual.reshape(-1, d_model)
         out = ops.linear(ctx.reshape(-1, heads * d_head), self.W_O, res)
         return out.view(batch, seq, d_model)

@@ -57,6 +57,17 @@ def causal_attention(q, k, v, scale=None):
     return ref.causal_attention(q, k, v, scale)
 
 
+def qkv_attention(x, wq, wk, wv, heads: int, d_head: int, scale: float):
+    """x [B, S, d] -> causal multi-head attention context [B, S, H*Dh] (q/k/v projections fused)."""
+    if use_native("attention", x):
+        from nanotitan_b200.ops import native
+
+        return native.qkv_attention(x, wq, wk, wv, heads, d_head, scale)
+    b, s, _ = x.shape
+    q, k, v = (ref.linear(x, w).view(b, s, heads, d_head) for w in (wq, wk, wv))
+    return ref.causal_attention(q, k, v, scale).reshape(b, s, heads * d_head)
+
+
 def cross_entropy(logits, targets):
     if use_native("cross_entropy", logits, any_dtype=True):
         from nanotitan_b200.ops import native
@@ -80,6 +91,7 @@ __all__ = [
     "layer_norm",
     "linear",
     "causal_attention",
+    "qkv_attention",
     "cross_entropy",
     "linear_cross_entropy",
 ]

@@ -36,3 +36,34 @@ class _Flash(torch.autograd.Function):
 
 def flash_attention(q, k, v, scale):
     return _Flash.apply(q, k, v, scale)
+
+
+class _FlashQKV(torch.autograd.Function):
+    """Attention over a fused projection buffer qkv [B, S, 3*H*Dh] (q | k | v side by side); the
+    backward kernels write dq, dk, dv straight into the thirds of one dQKV buffer."""
+
+    @staticmethod
+    def forward(ctx, qkv, heads, d_head, scale):
+        b, s, _ = qkv.shape
+        inner = heads * d_head
+        q, k, v = (qkv[..., i * inner : (i + 1) * inner].view(b, s, heads, d_head) for i in range(3))
+        out, lse = get_ext().flash_fwd(q, k, v, scale)
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.meta = (heads, d_head, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse = ctx.saved_tensors
+        heads, d_head, scale = ctx.meta
+        b, s, _ = qkv.shape
+        inner = heads * d_head
+        dqkv = torch.empty_like(qkv)
+        q, k, v = (qkv[..., i * inner : (i + 1) * inner].view(b, s, heads, d_head) for i in range(3))
+        grads = [dqkv[..., i * inner : (i + 1) * inner].view(b, s, heads, d_head) for i in range(3)]
+        get_ext().flash_bwd(dout.contiguous(), q, k, v, out, lse, scale, grads)
+        return dqkv, None, None, None
+
+
+def flash_attention_qkv(qkv, heads, d_head, scale):
+    return _FlashQKV.apply(qkv, heads, d_head, scale)

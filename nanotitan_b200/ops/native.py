@@ -67,8 +67,66 @@ class _Linear(torch.autograd.Function):
             dx = dx.view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
             dw = torch.empty_like(w)
-            gemm_tc(x2, True, [dy2], True, [dw])  # x^T dy: both operands MN-major
+            wgrad(x2, dy2, [dw])  # x^T dy: both operands MN-major, split over the token dim
         return dx, dw, (dy if ctx.has_res else None)
+
+
+_UNIT_OFFSETS: dict = {}
+
+
+def whole_segment(rows: int, device) -> torch.Tensor:
+    """Offsets [0, rows]: a dense weight-gradient GEMM run as a one-segment ragged reduction, which
+    lets the kernel split the long reduction over the whole GPU."""
+    key = (rows, str(device))
+    if key not in _UNIT_OFFSETS:
+        _UNIT_OFFSETS[key] = torch.tensor([0, rows], dtype=torch.int32, device=device)
+    return _UNIT_OFFSETS[key]
+
+
+def wgrad(x2, dy2, outs):
+    """outs[i] = x2^T @ dy2[:, i-th column block]; reduction over the (long) row dim, split-K."""
+    gemm_tc(x2, True, [dy2], True, [o.unsqueeze(0) for o in outs], mode=GROUPED_K,
+            offsets=whole_segment(x2.shape[0], x2.device))
+
+
+class _QKVProjection(torch.autograd.Function):
+    """[q | k | v] = x @ [W_Q | W_K | W_V] as one GEMM over three weight tensors; backward is one
+    dgrad GEMM with the three weights stacked along the reduction and one wgrad GEMM writing the
+    three weight gradients."""
+
+    @staticmethod
+    def forward(ctx, x, wq, wk, wv):
+        x2 = _rows(x)
+        qkv = torch.empty(x2.shape[0], 3 * wq.shape[1], dtype=x.dtype, device=x.device)
+        gemm_tc(x2, False, [wq, wk, wv], True, [qkv], b_split=B_SPLIT_N)
+        ctx.save_for_backward(x2, wq, wk, wv)
+        ctx.x_shape = x.shape
+        return qkv.view(*x.shape[:-1], qkv.shape[1])
+
+    @staticmethod
+    def backward(ctx, dqkv):
+        x2, wq, wk, wv = ctx.saved_tensors
+        d2 = _rows(dqkv)
+        dx = torch.empty_like(x2)
+        gemm_tc(d2, False, [wq, wk, wv], False, [dx], b_split=B_SPLIT_K)
+        dws = [torch.empty_like(w) for w in (wq, wk, wv)]
+        wgrad(x2, d2, dws)
+        return dx.view(ctx.x_shape), dws[0], dws[1], dws[2]
+
+
+def qkv_attention(x, wq, wk, wv, heads, d_head, scale):
+    """x [B, S, d] -> attention context [B, S, H*Dh] (before the output projection)."""
+    from nanotitan_b200.ops import flash
+
+    inner = heads * d_head
+    fused = (tc_ok(x.reshape(-1, x.shape[-1]), wq, wk, wv) and wq.shape == wk.shape == wv.shape
+             and inner % 64 == 0 and d_head in (32, 64) and hasattr(get_ext(), "flash_fwd"))
+    if fused:
+        qkv = _QKVProjection.apply(x, wq, wk, wv)
+        return flash.flash_attention_qkv(qkv, heads, d_head, scale).reshape(*x.shape[:-1], inner)
+    b, s, _ = x.shape
+    q, k, v = (linear(x, w).view(b, s, heads, d_head) for w in (wq, wk, wv))
+    return causal_attention(q, k, v, scale).reshape(b, s, inner)
 
 
 def linear(x, w, residual=None):
