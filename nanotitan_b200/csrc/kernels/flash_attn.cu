@@ -29,6 +29,8 @@
 #include "sm100.cuh"
 #include "tma_desc.h"
 
+#include <type_traits>
+
 namespace nt {
 namespace flash {
 
@@ -52,7 +54,7 @@ struct Args {
 
 template <int DH, int MODE>
 struct Cfg {
-  static constexpr int BC = MODE == kFwd ? 128 : 64;            // streamed rows per step
+  static constexpr int BC = 64;                                 // streamed rows per step
   static constexpr int R_TILE = BR * DH * 2;                     // bytes
   static constexpr int C_TILE = BC * DH * 2;
   static constexpr int N_R = MODE == kFwd ? 1 : 2;
@@ -66,6 +68,7 @@ struct Cfg {
   static constexpr int OFF_BAR = OFF_VEC + (MODE == kDkv ? STAGES * 2 * BC * 4 : 0);
   static constexpr int TOTAL = OFF_BAR + 16 * 8 + 16 + 1024;
   static constexpr uint32_t TMEM_COLS = 256;
+  // forward double-buffers T1 (columns 0 and 64); backward keeps T1 at 0 and T2 at 64
   static constexpr uint32_t COL_T1 = 0, COL_T2 = BC, COL_ACC1 = 128, COL_ACC2 = 192;
   static constexpr uint32_t SWZ = DH == 32 ? 4u : 2u;            // 64-byte or 128-byte swizzle for [rows][Dh] tiles
   static constexpr uint32_t ROW_BYTES = DH * 2;
@@ -126,7 +129,7 @@ __device__ __forceinline__ void store_row(void* base, long long off, const float
 // tm0/tm1: resident tensors (box {Dh, 128, 1, 1}); tm2/tm3: streamed tensors (box {Dh, BC, 1, 1}).
 // Tensor maps are 4-D over (Dh, H, S, B) so a tile is addressed as (0, h, s0, b).
 template <int DH, int MODE>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)
 flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1,
              const __grid_constant__ CUtensorMap tm2, const __grid_constant__ CUtensorMap tm3, const Args args) {
   using namespace sm100;
@@ -139,7 +142,8 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
   uint64_t* r_full = bars;            // 1
   uint64_t* c_full = bars + 1;        // 2
   uint64_t* c_empty = bars + 3;       // 2
-  uint64_t* t_full = bars + 5;        // 1
+  uint64_t* t_full = bars + 5;        // 1 (forward: buffer 0)
+  uint64_t* t_full_b = bars + 9;      // forward: buffer 1
   uint64_t* e_full = bars + 6;        // 1 (128 arrivals)
   uint64_t* e_empty = bars + 7;       // 1
   uint64_t* acc_full = bars + 8;      // 1
@@ -161,12 +165,15 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
     c_begin = 0;
     c_end = (min(r0 + BR, S) + BC - 1) / BC;             // keys <= last query of the tile
   }
-  const int n_iter = c_end - c_begin;
+  // a failure recorded earlier (by any kernel) turns every later CTA into a no-op until the host clears it
+  const bool dead = args.status != nullptr && *reinterpret_cast<volatile uint32_t*>(&args.status->code) != 0u;
+  const int n_iter = dead ? 0 : c_end - c_begin;
 
   if (threadIdx.x == 0) {
     mbar_init(r_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&c_full[s], 1); mbar_init(&c_empty[s], 1); }
     mbar_init(t_full, 1);
+    mbar_init(t_full_b, 1);
     mbar_init(e_full, 128);
     mbar_init(e_empty, 1);
     mbar_init(acc_full, 1);
@@ -210,9 +217,45 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
     const uint32_t ra = smem_u32(smem + C::OFF_R), rb = ra + C::R_TILE;
     const uint32_t e1 = smem_u32(smem + C::OFF_E), e2 = e1 + C::E_TILE;
     bool ok = mbar_wait(r_full, 0, abort_flag, args.status, kKernelAttnFwd + MODE, 200);
+    if (MODE == kFwd) {
+      // Forward keeps two score buffers in TMEM: the scores of step it+1 are issued before the
+      // softmax threads have finished step it, so they never wait for the tensor core.
+      auto issue_scores = [&](int it) -> bool {
+        const int st = it & 1;
+        if (!mbar_wait(&c_full[st], (it >> 1) & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 210 + st)) return false;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t ca = smem_u32(smem + C::OFF_C + st * 2 * C::C_TILE);
+#pragma unroll
+          for (int ks = 0; ks < DH / 16; ++ks)
+            umma_f16(tmem_base + C::COL_T1 + st * BC, make_desc(ra + ks * 32, 16, C::SBO_RC, C::SWZ),
+                     make_desc(ca + ks * 32, 16, C::SBO_RC, C::SWZ), idesc_t, ks != 0);
+          umma_commit(st ? t_full_b : t_full);
+        }
+        __syncwarp();
+        return true;
+      };
+      if (ok && n_iter > 0) ok = issue_scores(0);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        if (it + 1 < n_iter && !issue_scores(it + 1)) { ok = false; break; }
+        if (!mbar_wait(e_full, it & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 220)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const int st = it & 1;
+          const uint32_t cb = smem_u32(smem + C::OFF_C + st * 2 * C::C_TILE) + C::C_TILE;  // V
+#pragma unroll
+          for (int ks = 0; ks < BC / 16; ++ks)
+            umma_f16(tmem_base + C::COL_ACC1, make_desc(e1 + ks * 32, 16, 1024, 2u),
+                     make_desc(cb + ks * 2 * C::SBO_RC, 16, C::SBO_RC, C::SWZ), idesc_acc, ks != 0 ? 1u : 0u);
+          umma_commit(&c_empty[st]);
+          umma_commit(acc_full);
+        }
+        __syncwarp();
+      }
+    }
     int stage = 0;
     uint32_t phase = 0;
-    for (int it = 0; it < n_iter && ok; ++it) {
+    for (int it = 0; it < n_iter && ok && MODE != kFwd; ++it) {
       if (!mbar_wait(&c_full[stage], phase, abort_flag, args.status, kKernelAttnFwd + MODE, 210 + stage)) { ok = false; break; }
       tc_fence_after();
       const uint32_t ca = smem_u32(smem + C::OFF_C + stage * 2 * C::C_TILE), cb = ca + C::C_TILE;
@@ -281,8 +324,77 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
       my_dsum = args.dsum[bh * S + row_idx];
     }
     bool ok = true;
+    if (MODE == kFwd) {
+      float alpha_prev = 0.f;
+      // fold the P.V product of step `it` (already rescaled relative to that step's row max)
+      auto fold_pv = [&](int it) -> bool {
+        if (!mbar_wait(acc_full, it & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 320)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int cc = 0; cc < DH; cc += 32) {
+          uint32_t t[32];
+          tmem_ld_32x32(lane_addr + C::COL_ACC1 + cc, t);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[cc + i] = o_acc[cc + i] * alpha_prev + __uint_as_float(t[i]);
+        }
+        tc_fence_before();
+        return true;
+      };
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int c0 = it * BC;
+        if (!mbar_wait((it & 1) ? t_full_b : t_full, (it >> 1) & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 300)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t t[BC];
+        {
+          uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&t[0]);
+          uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&t[32]);
+          tmem_ld_32x32(lane_addr + C::COL_T1 + (it & 1) * BC, lo);
+          tmem_ld_32x32(lane_addr + C::COL_T1 + (it & 1) * BC + 32, hi);
+          tmem_ld_wait();
+        }
+        tc_fence_before();
+        // tiles left of the diagonal and inside the sequence need no mask (uniform over the CTA)
+        const bool need_mask = (c0 + BC - 1 > r0) || (c0 + BC > S);
+        float m_new = m_run;
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < BC; ++i) {
+            const int key = c0 + i;
+            if (!(key <= row_idx && key < S)) t[i] = 0xff800000u;  // -inf
+            m_new = fmaxf(m_new, __uint_as_float(t[i]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < BC; ++i) m_new = fmaxf(m_new, __uint_as_float(t[i]));
+        }
+        const float alpha = exp2f((m_run - m_new) * sl2);  // first tile: m_run = -inf -> 0
+        const float shift = m_new * sl2;
+        float l_add = 0.f;
+#pragma unroll
+        for (int i = 0; i < BC; ++i) {
+          const float pi = exp2f(fmaf(__uint_as_float(t[i]), sl2, -shift));  // exp2(-inf) = 0 for masked entries
+          l_add += pi;
+          t[i] = __float_as_uint(pi);  // probabilities replace the scores in place
+        }
+        // the previous step's P.V finished long ago; folding it here keeps its latency off the loop
+        if (it > 0 && !fold_pv(it - 1)) { ok = false; break; }
+        {
+          float (&plo)[32] = *reinterpret_cast<float (*)[32]>(&t[0]);
+          float (&phi)[32] = *reinterpret_cast<float (*)[32]>(&t[32]);
+          write_e_chunk(e1, r, 0, plo, args.dtype);
+          write_e_chunk(e1, r, 32, phi, args.dtype);
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(e_full);
+        l_run = l_run * alpha + l_add;
+        m_run = m_new;
+        alpha_prev = alpha;
+      }
+      if (ok && n_iter > 0) ok = fold_pv(n_iter - 1);
+    }
     int stage = 0;
-    for (int it = 0; it < n_iter && ok; ++it) {
+    for (int it = 0; it < n_iter && ok && MODE != kFwd; ++it) {
       const int c0 = (c_begin + it) * BC;  // first streamed index (key for fwd/dq, query for dkv)
       if (MODE == kDkv) {
         // stage the streamed queries' lse / dsum in shared memory (values past S are neutral)
@@ -299,89 +411,46 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
       if (it > 0) {
         if (!mbar_wait(e_empty, (it - 1) & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 310)) { ok = false; break; }
       }
-      if (MODE == kFwd) {
-        // ---- pass 1: row max of this tile
-        float m_new = m_run;
-#pragma unroll 1
-        for (int cc = 0; cc < BC; cc += 32) {
-          uint32_t t[32];
-          tmem_ld_32x32(lane_addr + C::COL_T1 + cc, t);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = c0 + cc + i;
-            const float s = (key <= row_idx && key < S) ? __uint_as_float(t[i]) : -INFINITY;
-            m_new = fmaxf(m_new, s);
-          }
-        }
-        const float alpha = exp2f((m_run - m_new) * sl2);  // m_run = -inf on the first tile -> 0
-        float l_add = 0.f;
-        // ---- pass 2: probabilities -> E
-#pragma unroll 1
-        for (int cc = 0; cc < BC; cc += 32) {
-          uint32_t t[32];
-          tmem_ld_32x32(lane_addr + C::COL_T1 + cc, t);
-          tmem_ld_wait();
-          float p[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = c0 + cc + i;
-            const bool keep = key <= row_idx && key < S;
-            p[i] = keep ? exp2f((__uint_as_float(t[i]) - m_new) * sl2) : 0.f;
-            l_add += p[i];
-          }
-          write_e_chunk(e1, r, cc, p, args.dtype);
-        }
-        fence_proxy_async_smem();
-        tc_fence_before();
-        mbar_arrive(e_full);
-        l_run = l_run * alpha + l_add;
-        m_run = m_new;
-        if (!mbar_wait(acc_full, it & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 320)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int cc = 0; cc < DH; cc += 32) {
-          uint32_t t[32];
-          tmem_ld_32x32(lane_addr + C::COL_ACC1 + cc, t);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o_acc[cc + i] = o_acc[cc + i] * alpha + __uint_as_float(t[i]);
-        }
-        tc_fence_before();
-      } else {
+      {
         const float* vl = vec + stage * 2 * BC;
+        // only tiles that straddle the diagonal or the end of the sequence need the mask (uniform)
+        const bool need_mask = (MODE == kDq) ? ((c0 + BC - 1 > r0) || (c0 + BC > S)) : ((r0 + BR - 1 > c0) || (c0 + BC > S));
+        auto process = [&](auto mask_tag) {
+          constexpr bool MASK = decltype(mask_tag)::value;
 #pragma unroll 1
-        for (int cc = 0; cc < BC; cc += 32) {
-          uint32_t t1[32], t2[32];
-          tmem_ld_32x32(lane_addr + C::COL_T1 + cc, t1);
-          tmem_ld_32x32(lane_addr + C::COL_T2 + cc, t2);
-          tmem_ld_wait();
-          float pv[32], ds[32];
+          for (int cc = 0; cc < BC; cc += 32) {
+            uint32_t t1[32], t2[32];
+            tmem_ld_32x32(lane_addr + C::COL_T1 + cc, t1);
+            tmem_ld_32x32(lane_addr + C::COL_T2 + cc, t2);
+            tmem_ld_wait();
+            float pv[32], ds[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int ci = c0 + cc + i;
-            bool keep;
-            float lse2, dsum;
-            if (MODE == kDq) {          // row = query, column = key
-              keep = ci <= row_idx && ci < S;
-              lse2 = my_lse;
-              dsum = my_dsum;
-            } else {                    // row = key, column = query
-              keep = row_idx <= ci && ci < S;
-              lse2 = vl[cc + i];
-              dsum = vl[BC + cc + i];
+            for (int i = 0; i < 32; ++i) {
+              const int ci = c0 + cc + i;
+              bool keep = true;
+              float lse2, dsum;
+              if (MODE == kDq) {          // row = query, column = key
+                if (MASK) keep = ci <= row_idx && ci < S;
+                lse2 = my_lse;
+                dsum = my_dsum;
+              } else {                    // row = key, column = query
+                if (MASK) keep = row_idx <= ci && ci < S;
+                lse2 = vl[cc + i];
+                dsum = vl[BC + cc + i];
+              }
+              const float p = keep ? exp2f(fmaf(__uint_as_float(t1[i]), sl2, -lse2)) : 0.f;
+              pv[i] = p;
+              ds[i] = p * (__uint_as_float(t2[i]) - dsum) * args.scale;
             }
-            const float p = keep ? exp2f(__uint_as_float(t1[i]) * sl2 - lse2) : 0.f;
-            pv[i] = p;
-            ds[i] = p * (__uint_as_float(t2[i]) - dsum) * args.scale;
+            if (MODE == kDq) {
+              write_e_chunk(e1, r, cc, ds, args.dtype);
+            } else {
+              write_e_chunk(e1, r, cc, pv, args.dtype);
+              write_e_chunk(e2, r, cc, ds, args.dtype);
+            }
           }
-          if (MODE == kDq) {
-            write_e_chunk(e1, r, cc, ds, args.dtype);
-          } else {
-            write_e_chunk(e1, r, cc, pv, args.dtype);
-            write_e_chunk(e2, r, cc, ds, args.dtype);
-          }
-        }
+        };
+        if (need_mask) process(std::true_type{}); else process(std::false_type{});
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(e_full);
@@ -394,7 +463,7 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
     if (ok && MODE != kFwd && n_iter > 0) ok = mbar_wait(acc_full, 0, abort_flag, args.status, kKernelAttnFwd + MODE, 330);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
-    if (ok && row_idx < S) {
+    if (ok && n_iter > 0 && row_idx < S) {
       const long long off = static_cast<long long>(b) * args.o_sb + static_cast<long long>(row_idx) * args.o_ss +
                             static_cast<long long>(h) * args.o_sh;
       if (MODE == kFwd) {
@@ -517,7 +586,7 @@ std::vector<at::Tensor> flash_fwd(const at::Tensor& q, const at::Tensor& k, cons
   a.out0 = out.data_ptr(); a.o_sb = out.stride(0); a.o_ss = out.stride(1); a.o_sh = out.stride(2);
   a.lse = lse.data_ptr<float>();
   a.status = device_status_word();
-  const CUtensorMap mq = map_bshd(q, BR), mk = map_bshd(k, 128), mv = map_bshd(v, 128);
+  const CUtensorMap mq = map_bshd(q, BR), mk = map_bshd(k, 64), mv = map_bshd(v, 64);
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   if (DH == 32) launch<32, kFwd>(mq, mq, mk, mv, a, stream); else launch<64, kFwd>(mq, mq, mk, mv, a, stream);
   return {out, lse};

@@ -265,6 +265,7 @@ void gemm_tc(const at::Tensor& A, bool a_mn, const std::vector<at::Tensor>& Bs, 
   else m_tiles = args.G * ((args.M + gemm::BM - 1) / gemm::BM);
 
   int bn = epilogue == gemm::kEpiSwigluFwd ? 256 : pick_bn(m_tiles, args.N, sms);
+  if (mode == gemm::kGroupedK && args.N >= 256) bn = 256;  // split-K fills the GPU; keep the wide tile
   if (force_bn > 0) bn = static_cast<int>(force_bn);
   TORCH_CHECK(bn == 64 || bn == 128 || bn == 256, "BN must be 64, 128 or 256");
   if (b_split == gemm::kBSplitN) {

@@ -283,7 +283,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int n_total = total_tiles<BN, EPI>(args, tile_start);
+  // a failure recorded earlier (by any kernel) turns every later CTA into a no-op until the host clears it
+  const bool dead = args.status != nullptr && *reinterpret_cast<volatile uint32_t*>(&args.status->code) != 0u;
+  const int n_total = dead ? 0 : total_tiles<BN, EPI>(args, tile_start);
   const uint32_t idesc = umma_idesc(args.dtype, BM, BN, args.a_mn, args.b_mn);
 
   if (warp == 0) {

@@ -51,7 +51,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // time-out per CTA and the kernel still runs to its end (where TMEM is released).
 // Returns false when the wait was abandoned.
 #ifndef NT_WAIT_LIMIT_CYCLES
-#define NT_WAIT_LIMIT_CYCLES (4000000000ll)  // about 2 s at 2 GHz
+#define NT_WAIT_LIMIT_CYCLES (400000000ll)  // about 0.2 s at 2 GHz
 #endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           StatusWord* status, uint32_t kernel_id, uint32_t detail) {
