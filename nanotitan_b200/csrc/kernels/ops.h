@@ -54,6 +54,13 @@ std::vector<at::Tensor> flash_fwd(const at::Tensor& q, const at::Tensor& k, cons
 std::vector<at::Tensor> flash_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                   const at::Tensor& out, const at::Tensor& lse, double scale, const std::vector<at::Tensor>& grads);
 
+// ---- fused gradient-bucket all-reduce (+ AdamW) over NVLink peer / multicast memory (allreduce_adamw.cu)
+void bucket_allreduce(at::Tensor grad_local, int64_t grad_mc, const at::Tensor& grad_peers, int64_t param_mc,
+                      const at::Tensor& param_peers, const c10::optional<at::Tensor>& master, const c10::optional<at::Tensor>& m,
+                      const c10::optional<at::Tensor>& v, at::Tensor flag_local, const at::Tensor& flag_peers, at::Tensor block_counter,
+                      int64_t rank, int64_t world, int64_t slot, int64_t epoch, int64_t step, double lr, double beta1, double beta2,
+                      double eps, double wd, int64_t blocks, double wait_ms);
+
 // ---- MoE routing / dispatch
 std::vector<at::Tensor> router_topk(const at::Tensor& x, const at::Tensor& w, int64_t k);
 std::vector<at::Tensor> assign_slots(const at::Tensor& idx, const at::Tensor& counts);

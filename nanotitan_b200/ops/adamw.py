@@ -17,11 +17,16 @@ from nanotitan_b200.parallel.reducer import ReducerV1
 
 
 class _Chunk:
-    def __init__(self, bucket, params, spans):
+    def __init__(self, bucket, params, spans, engine=None):
         self.bucket = bucket
         self.params, self.spans = params, spans
+        self.fused_by_engine = False
         n = bucket.buffer.numel()
-        flat = torch.zeros(n, dtype=bucket.dtype, device=bucket.device)
+        if engine is not None:
+            flat = engine.alloc(n, bucket.dtype, bucket.device)  # symmetric: peers write new values into it
+            flat.zero_()
+        else:
+            flat = torch.zeros(n, dtype=bucket.dtype, device=bucket.device)
         for p, (lo, hi) in zip(params, spans):
             flat[lo:hi].copy_(p.data.reshape(-1))
             p.data = flat[lo:hi].view_as(p)
@@ -50,13 +55,22 @@ class FusedAdamW(torch.optim.Optimizer):
         self._chunks = []
         for red in reducers.values():
             for b in red.buckets:
-                self._chunks.append(_Chunk(b, b.params, b.spans))
+                engine = red._engine_for(b) if hasattr(red, "_engine_for") else None
+                chunk = _Chunk(b, b.params, b.spans, engine)
+                if engine is not None:
+                    engine.bind_optimizer(b, chunk.flat_param, chunk.master, chunk.exp_avg, chunk.exp_avg_sq, self)
+                    chunk.fused_by_engine = True
+                self._chunks.append(chunk)
                 owned.update(id(p) for p in b.params)
         rest = [p for p in self._params if id(p) not in owned]
         if rest:
             self._own_reducer = ReducerV1(rest, 1, None, bucket_size=1 << 20)
             for b in self._own_reducer.buckets:
                 self._chunks.append(_Chunk(b, b.params, b.spans))
+
+    def next_step(self) -> int:
+        """Step number the update in flight belongs to (bucket kernels run before `step()`)."""
+        return self._step + 1
 
     def _ensure_layout(self) -> None:
         if self._chunks is None:
@@ -76,6 +90,9 @@ class FusedAdamW(torch.optim.Optimizer):
         beta1, beta2 = group["betas"]
         self._sq_parts = []
         for c in self._chunks:
+            if c.fused_by_engine and c.bucket.launched_this_step:
+                c.bucket.launched_this_step = False  # updated by the all-reduce kernel already
+                continue
             grads = c.bucket.buffer
             for p, (lo, hi) in zip(c.params, c.spans):  # a gradient that is not the bucket view
                 if p.grad is not None and p.grad.data_ptr() != grads[lo:hi].data_ptr():

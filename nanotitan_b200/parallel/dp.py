@@ -36,17 +36,22 @@ class DataParallel:
             groups["expert"], self.dims.expert_dp_group_ranks[0], self.dims.expert_dp_group
         )
         bucket = self.cfg.runtime.bucket_size
-        self.shared_reducer = ReducerV1(
-            groups["shared"], len(self.dims.shared_dp_group_ranks), self.dims.shared_dp_group, bucket
-        )
-        self.expert_reducer = ReducerV1(
-            groups["expert"], len(self.dims.expert_dp_group_ranks), self.dims.expert_dp_group, bucket
-        )
+        shared_engine = expert_engine = None
         if self.device.type == "cuda":
             from nanotitan_b200.parallel import fused_allreduce
 
-            fused_allreduce.attach_if_possible(self.shared_reducer)
-            fused_allreduce.attach_if_possible(self.expert_reducer)
+            shared_engine = fused_allreduce.make_engine(
+                self.dims.shared_dp_group, len(self.dims.shared_dp_group_ranks), self.device)
+            expert_engine = fused_allreduce.make_engine(
+                self.dims.expert_dp_group, len(self.dims.expert_dp_group_ranks), self.device)
+        self.shared_reducer = ReducerV1(
+            groups["shared"], len(self.dims.shared_dp_group_ranks), self.dims.shared_dp_group, bucket,
+            engine=shared_engine,
+        )
+        self.expert_reducer = ReducerV1(
+            groups["expert"], len(self.dims.expert_dp_group_ranks), self.dims.expert_dp_group, bucket,
+            engine=expert_engine,
+        )
         return model
 
     def broadcast_parameters(self, params, src_rank: int, group, async_op: bool = False) -> None:

@@ -37,6 +37,7 @@ class Bucket:
     work: object | None = None
     buffer: torch.Tensor | None = None  # flat gradients; every param.grad views into it
     launched: bool = False
+    launched_this_step: bool = False  # consumed by a bound optimizer
 
 
 def plan_buckets(params, bucket_bytes: int) -> list[Bucket]:
@@ -61,15 +62,15 @@ def plan_buckets(params, bucket_bytes: int) -> list[Bucket]:
 
 
 class ReducerV1:
-    def __init__(self, params, group_size: int, process_group, bucket_size: int, allocator=None):
+    def __init__(self, params, group_size: int, process_group, bucket_size: int, allocator=None, engine=None):
         self.group_size = group_size
         self.process_group = process_group
         self.params = [p for p in params if p.requires_grad]
         self.bucket_size = bucket_size * 1024 * 1024
         self.backward_grad_sync = False
         self.ready_for_sync: set[nn.Parameter] = set()
-        self.bucket_engine = None  # set by fused_allreduce.attach(...)
-        self._allocator = allocator
+        self.bucket_engine = engine  # fused all-reduce (+ AdamW) kernels; None = dist.all_reduce
+        self._allocator = allocator if engine is None else engine.alloc
         self.initialize_buckets()
         self.hook_handles = [
             p.register_post_accumulate_grad_hook(self.reduce_grad) for p in self.params
@@ -124,7 +125,8 @@ class ReducerV1:
 
     def _launch(self, bucket: Bucket) -> None:
         bucket.launched = True
-        if self.bucket_engine is not None:
+        bucket.launched_this_step = True
+        if self._engine_for(bucket) is not None:
             bucket.work = self.bucket_engine.launch(self, bucket)
         elif self.group_size > 1:
             bucket.work = dist.all_reduce(
@@ -132,6 +134,12 @@ class ReducerV1:
             )
         else:
             bucket.work = None
+
+    def _engine_for(self, bucket: Bucket):
+        """The fused kernels take 16-bit buckets; anything else stays on dist.all_reduce."""
+        if self.bucket_engine is not None and bucket.dtype in (torch.bfloat16, torch.float16):
+            return self.bucket_engine
+        return None
 
     def prepare_missing_grad(self) -> None:
         """Fire the hook of parameters autograd never reached (their grad view is already zero)."""
@@ -145,7 +153,7 @@ class ReducerV1:
         for bucket in self.buckets:
             if not bucket.launched:
                 continue
-            if self.bucket_engine is not None:
+            if self._engine_for(bucket) is not None:
                 self.bucket_engine.finish(self, bucket)
             else:
                 if bucket.work is not None:

@@ -35,12 +35,18 @@ def _repo_cwd(monkeypatch):
     monkeypatch.chdir(ROOT)
 
 
-def _worker(rank, world_size, init_file, fn, args, err_dir):
+def _worker(rank, world_size, init_file, fn, args, err_dir, backend="gloo"):
     import torch.distributed as dist
 
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world_size))
     try:
-        dist.init_process_group("gloo", init_method=f"file://{init_file}", rank=rank, world_size=world_size)
+        if backend == "nccl":
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", init_method=f"file://{init_file}", rank=rank, world_size=world_size,
+                                    device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", init_method=f"file://{init_file}", rank=rank, world_size=world_size)
         fn(rank, world_size, *args)
     except Exception:
         Path(err_dir, f"rank{rank}.err").write_text(traceback.format_exc())
@@ -50,13 +56,14 @@ def _worker(rank, world_size, init_file, fn, args, err_dir):
             dist.destroy_process_group()
 
 
-def run_distributed(fn, world_size: int, *args, timeout: float = 240.0):
-    """Run `fn(rank, world_size, *args)` on `world_size` gloo ranks; re-raise the first failure."""
+def run_distributed(fn, world_size: int, *args, timeout: float = 240.0, backend: str = "gloo"):
+    """Run `fn(rank, world_size, *args)` on `world_size` ranks (gloo on CPU, or nccl with one GPU
+    per rank); re-raise the first failure."""
     import torch.multiprocessing as mp
 
     with tempfile.TemporaryDirectory() as tmp:
         init_file = os.path.join(tmp, "rdzv")
-        ctx = mp.spawn(_worker, args=(world_size, init_file, fn, args, tmp), nprocs=world_size, join=False)
+        ctx = mp.spawn(_worker, args=(world_size, init_file, fn, args, tmp, backend), nprocs=world_size, join=False)
         try:
             ok = ctx.join(timeout)
             while not ok:
