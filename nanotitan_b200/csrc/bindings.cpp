@@ -35,6 +35,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("flash_bwd", &nt::flash_bwd, py::arg("dout"), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("lse"),
         py::arg("scale"), py::arg("grads") = std::vector<at::Tensor>{}, "Causal flash attention backward -> (dq, dk, dv)");
   m.def("bucket_allreduce", &nt::bucket_allreduce, "Fused bucket all-reduce (+ AdamW) over peer / multicast memory");
+  m.def("ep_allgather_counts", &nt::ep_allgather_counts, "All-gather per-expert counts through peer stores");
+  m.def("ep_push_rows", &nt::ep_push_rows, "Push rows into peers' staging buffers (expert-parallel dispatch / return)");
   m.def("layer_norm_fwd", &nt::layer_norm_fwd);
   m.def("layer_norm_bwd", &nt::layer_norm_bwd);
   m.def("cross_entropy_fwd_bwd", &nt::cross_entropy_fwd_bwd);

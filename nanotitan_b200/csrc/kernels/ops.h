@@ -61,6 +61,13 @@ void bucket_allreduce(at::Tensor grad_local, int64_t grad_mc, const at::Tensor& 
                       int64_t rank, int64_t world, int64_t slot, int64_t epoch, int64_t step, double lr, double beta1, double beta2,
                       double eps, double wd, int64_t blocks, double wait_ms);
 
+// ---- expert-parallel row exchange over NVLink peer memory (ep_exchange.cu)
+void ep_allgather_counts(const at::Tensor& counts, const at::Tensor& cmat_peers, at::Tensor flag_local, const at::Tensor& flag_peers,
+                         int64_t rank, int64_t world, int64_t epoch, int64_t word_base, double wait_ms);
+void ep_push_rows(const at::Tensor& src, const at::Tensor& dst_peers, int64_t dst_capacity_rows, const at::Tensor& cmat, int64_t E_loc,
+                  int64_t direction, at::Tensor block_counter, at::Tensor flag_local, const at::Tensor& flag_peers, int64_t rank,
+                  int64_t world, int64_t epoch, int64_t word_base, double wait_ms, int64_t blocks);
+
 // ---- MoE routing / dispatch
 std::vector<at::Tensor> router_topk(const at::Tensor& x, const at::Tensor& w, int64_t k);
 std::vector<at::Tensor> assign_slots(const at::Tensor& idx, const at::Tensor& counts);

@@ -53,7 +53,12 @@ def expert_parallel_moe(backend, flat: torch.Tensor, residual: torch.Tensor | No
         gates, top_e, probs, counts = native.router_topk(flat, backend.router.weight, cfg.top_k)
     with nvtx_range("moe/pack_tokens"):
         packed_x, packed_gate, packed_token, _, _, slot_of = native.pack(flat, gates, top_e, counts)
-    fused = getattr(backend, "fused_exchange", None)
+    if not hasattr(backend, "fused_exchange"):
+        from nanotitan_b200.parallel import ep_fused
+
+        ok = flat.dtype in (torch.bfloat16, torch.float16) and flat.shape[1] % 8 == 0
+        backend.fused_exchange = ep_fused.get_exchange(backend.spec.ep_group, cfg.num_experts, flat.device) if ok else None
+    fused = backend.fused_exchange
     with nvtx_range("moe/dispatch"):
         if fused is not None:
             expert_in, local_offsets, ctx = fused.dispatch(packed_x, counts)

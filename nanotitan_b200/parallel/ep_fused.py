@@ -1,0 +1,139 @@
+"""Expert-parallel dispatch / return with kernels that write straight into peer memory.
+
+`FusedExchange` holds, for one expert-parallel group, symmetric staging buffers (mapped into
+every peer), the all-gathered count matrix and a flag pad.  A layer's forward does:
+
+    counts --ep_allgather_counts--> C[src][expert]           (peer stores + flag barrier)
+    packed rows --ep_push_rows(0)--> expert ranks' staging    (already expert-major there)
+    ... grouped expert GEMMs ...
+    expert outputs --ep_push_rows(1)--> home ranks' staging   (already in packed order there)
+
+and backward runs the two pushes the other way round.  Compared with the NCCL path
+(`parallel/ep.py::_nccl_exchange`) there is no count collective, no split-size read-back for the
+collective, no send/receive buffers and no regrouping gather/scatter.  One 4-byte host read per
+layer remains: the number of rows this rank received, needed to size the activation tensors.
+Symmetric memory and its rendezvous come from `torch.distributed._symmetric_memory`.
+"""
+from __future__ import annotations
+
+import logging
+import os
+
+import torch
+import torch.distributed as dist
+
+from nanotitan_b200.ops.ext import get_ext
+
+logger = logging.getLogger(__name__)
+
+FLAG_WORDS = 64
+
+
+class FusedExchange:
+    def __init__(self, group, num_experts: int, device: torch.device):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.symm_mem, self.group, self.device = symm_mem, group, device
+        self.ep = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.E = num_experts
+        self.E_loc = num_experts // self.ep
+        self.wait_ms = float(os.environ.get("NT_COMM_WAIT_MS", "20000"))
+        self.blocks = int(os.environ.get("NT_EP_BLOCKS", "96"))
+        self._handles = {}
+        self.flags = self._alloc(FLAG_WORDS, torch.int32)
+        self.flags.zero_()
+        self.flag_peers = self._peers(self.flags)
+        self.cmat = self._alloc(self.ep * self.E, torch.int32).view(self.ep, self.E)
+        self.cmat.zero_()
+        self.cmat_peers = self._peers(self.cmat)
+        self.block_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = 0
+        self.staging: dict[int, torch.Tensor] = {}       # direction -> [capacity, d]
+        self.staging_peers: dict[int, torch.Tensor] = {}
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    def _alloc(self, numel, dtype):
+        t = self.symm_mem.empty(numel, dtype=dtype, device=self.device)
+        self._handles[t.data_ptr()] = self.symm_mem.rendezvous(t, self.group)
+        return t
+
+    def _peers(self, t):
+        return torch.tensor(list(self._handles[t.data_ptr()].buffer_ptrs), dtype=torch.int64)
+
+    def _staging_for(self, direction: int, rows: int, d: int, dtype) -> torch.Tensor:
+        """Staging buffer rows land in: direction 0 -> expert side (worst case ep * A rows),
+        direction 1 -> home side (A rows).  Every rank sees the same shapes, so (re)allocation
+        happens on all ranks at the same call."""
+        buf = self.staging.get(direction)
+        if buf is None or buf.shape[0] < rows or buf.shape[1] != d or buf.dtype != dtype:
+            flat = self._alloc(rows * d, dtype)
+            buf = flat.view(rows, d)
+            self.staging[direction] = buf
+            self.staging_peers[direction] = self._peers(flat)
+        return buf
+
+    def _next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    # ------------------------------------------------------------------ primitives
+    def allgather_counts(self, counts: torch.Tensor) -> torch.Tensor:
+        get_ext().ep_allgather_counts(counts.to(torch.int32).contiguous(), self.cmat_peers, self.flags, self.flag_peers,
+                                      self.rank, self.ep, self._next_epoch(), 0, self.wait_ms)
+        return self.cmat.clone()
+
+    def push(self, rows: torch.Tensor, cmat: torch.Tensor, direction: int, assignments: int, out_rows: int) -> torch.Tensor:
+        cap = self.ep * assignments if direction == 0 else assignments
+        staging = self._staging_for(direction, cap, rows.shape[1], rows.dtype)
+        get_ext().ep_push_rows(rows.contiguous(), self.staging_peers[direction], staging.shape[0], cmat, self.E_loc, direction,
+                               self.block_counter, self.flags, self.flag_peers, self.rank, self.ep, self._next_epoch(), 0,
+                               self.wait_ms, self.blocks)
+        return staging[:out_rows].clone()
+
+    # ------------------------------------------------------------------ layer interface (see parallel/ep.py)
+    def dispatch(self, packed_x: torch.Tensor, counts: torch.Tensor):
+        cmat = self.allgather_counts(counts)
+        mine = cmat[:, self.rank * self.E_loc : (self.rank + 1) * self.E_loc]
+        per_expert = mine.sum(dim=0)
+        local_offsets = torch.zeros(self.E_loc + 1, dtype=torch.int32, device=packed_x.device)
+        local_offsets[1:] = torch.cumsum(per_expert, dim=0)
+        received = int(local_offsets[-1].item())  # the layer's one host read
+        assignments = packed_x.shape[0]
+        expert_in = _Push.apply(packed_x, self, cmat, 0, assignments, received)
+        return expert_in, local_offsets, (cmat, assignments)
+
+    def gather_back(self, expert_out: torch.Tensor, ctx) -> torch.Tensor:
+        cmat, assignments = ctx
+        return _Push.apply(expert_out, self, cmat, 1, assignments, assignments)
+
+
+class _Push(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, rows, exchange, cmat, direction, assignments, out_rows):
+        ctx.exchange, ctx.cmat, ctx.direction, ctx.assignments, ctx.in_rows = exchange, cmat, direction, assignments, rows.shape[0]
+        return exchange.push(rows, cmat, direction, assignments, out_rows)
+
+    @staticmethod
+    def backward(ctx, grad):
+        back = ctx.exchange.push(grad, ctx.cmat, 1 - ctx.direction, ctx.assignments, ctx.in_rows)
+        return back, None, None, None, None, None
+
+
+_EXCHANGES: dict = {}
+
+
+def get_exchange(group, num_experts: int, device: torch.device):
+    """One `FusedExchange` per expert-parallel group (shared by all layers); None when disabled or
+    when symmetric memory cannot be set up (the NCCL path is used then)."""
+    if os.environ.get("NT_FUSED_EP", "1") == "0" or group is None:
+        return None
+    key = id(group)
+    if key not in _EXCHANGES:
+        try:
+            _EXCHANGES[key] = FusedExchange(group, num_experts, device)
+        except Exception as exc:  # noqa: BLE001
+            logger.warning("fused expert-parallel exchange unavailable (%s: %s); using NCCL", type(exc).__name__, exc)
+            _EXCHANGES[key] = None
+    return _EXCHANGES[key]

@@ -121,3 +121,51 @@ def _engine_worker(rank, world, multimem):
 def test_fused_bucket_allreduce_and_adamw(multimem):
     _need(2)
     run_distributed(_engine_worker, 2, multimem, backend="nccl")
+
+
+def _ep_compare_worker(rank, world):
+    import os
+
+    os.environ["NT_COMM_WAIT_MS"] = "3000"
+    import torch.distributed as dist
+
+    from nanotitan_b200.config import ModelConfig
+    from nanotitan_b200.models.feed_fwd import MoE
+    from nanotitan_b200.models.utils import ModelShardSpec
+    from nanotitan_b200.ops.ext import get_ext
+
+    dev = torch.device("cuda", rank)
+    cfg = ModelConfig(vocab_size=8, d_model=128, d_head=32, n_heads=4, n_layers=1, max_seq_len=64, ffn_in=256,
+                      num_experts=8, top_k=2, router_alpha=0.01, moe_backend="cuda", dtype="bfloat16")
+    per = cfg.num_experts // world
+    spec = ModelShardSpec(0, 1, False, False, False, per, rank * per, (rank + 1) * per, ep_size=world, ep_group=dist.group.WORLD)
+    torch.manual_seed(3)
+    moe = MoE(cfg, spec).to(dev)
+    with torch.no_grad():  # the router is replicated: same weights everywhere
+        dist.broadcast(moe.router.weight, src=0)
+        moe.router.weight.mul_(8.0)  # spread the routing
+    torch.manual_seed(100 + rank)
+    x = torch.randn(3, 64, 128, device=dev).bfloat16()
+    g = torch.randn_like(x)
+    results = []
+    for fused in (True, False):
+        xi = x.clone().requires_grad_()
+        moe.zero_grad(set_to_none=True)
+        if not fused:
+            moe.moe_backend.fused_exchange = None  # fall back to the NCCL all-to-all path
+        out, stats = moe(xi)
+        if fused:
+            assert moe.moe_backend.fused_exchange is not None, "symmetric memory could not be set up"
+        (out * g).sum().backward()
+        results.append([out.detach().clone(), xi.grad.clone()] + [p.grad.clone() for p in moe.experts.parameters()]
+                       + [stats.tokens_per_expert.clone()])
+    torch.cuda.synchronize()
+    assert get_ext().read_status(True)[0] == 0
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+    assert results[0][0].abs().max() > 0
+
+
+def test_fused_ep_exchange_equals_nccl_path():
+    _need(2)
+    run_distributed(_ep_compare_worker, 2, backend="nccl")
