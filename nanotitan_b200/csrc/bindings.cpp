@@ -47,6 +47,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("combine_fwd", &nt::combine_fwd);
   m.def("combine_bwd", &nt::combine_bwd);
   m.def("pack_bwd", &nt::pack_bwd);
+  m.def("bounded_wait_probe", &nt::bounded_wait_probe, "Let a bounded device wait run out; returns the number of threads that gave up");
   m.def("read_status", &nt::read_status, py::arg("clear") = true, "[code, kernel, detail, count] of the device status word");
   m.def("launch_count", [] { return static_cast<long long>(nt::launch_counter().load()); },
         "Kernels of this library launched by this process");

@@ -13,6 +13,8 @@ namespace nt {
 StatusWord* device_status_word();
 std::vector<int64_t> read_status(bool clear);  // [code, kernel, detail, count]
 
+int64_t bounded_wait_probe(double limit_ms);  // probe.cu: makes a bounded device wait run out, on purpose
+
 // ---- tcgen05 GEMM (gemm_tc.cu).
 //   A: 2-D; a_mn=false -> [M, K] rows contiguous in K, a_mn=true -> [K, M] rows contiguous in M.
 //   Bs: 1..3 tensors, 2-D or [G, ., .]; b_mn=false -> [N, K], b_mn=true -> [K, N].

@@ -1,0 +1,1 @@
+from nanotitan_b200.models.moe_ops import combine_tokens_fn, grouped_gemm_fn, pack_tokens_fn, torch_backend_all_to_all  # noqa: F401

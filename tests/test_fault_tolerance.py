@@ -1,0 +1,157 @@
+"""Failure detection, tested without faulting any GPU: failures are made on the host (a rank that
+raises, a rank that never joins), liveness travels through heartbeat files, a lost peer ends a
+collective through the process-group timeout, a device wait runs out on a flag nothing sets, and
+training resumes bit-exactly from a checkpoint."""
+import datetime
+import os
+import time
+
+import pytest
+import torch
+
+from tests.conftest import run_distributed
+from tests.helpers import fake_dims, full_spec, random_batch, tiny_app_cfg
+
+
+# ------------------------------------------------------------------ heartbeat
+def test_heartbeat_marks_stale_and_missing_ranks(tmp_path):
+    from nanotitan_b200.utils.heartbeat import Heartbeat, RankFailure, assert_peers_alive
+
+    a, b = Heartbeat(tmp_path, 0), Heartbeat(tmp_path, 1)
+    a.beat(3)
+    b.beat(3)
+    assert Heartbeat.stale_ranks(tmp_path, 3, max_age_s=60) == [2]  # rank 2 never wrote
+    assert Heartbeat.read(tmp_path, 1)["step"] == 3
+    later = time.time() + 120
+    assert Heartbeat.stale_ranks(tmp_path, 2, max_age_s=60, now=later) == [0, 1]
+    with pytest.raises(RankFailure, match=r"\[2\]"):
+        assert_peers_alive(tmp_path, 3, 60)
+
+
+def _lost_peer_worker(rank, world, hb_dir):
+    """Rank 1 leaves between steps (no collective in flight).  Rank 0 learns it from the heartbeat
+    before launching its next collective."""
+    import torch.distributed as dist
+
+    from nanotitan_b200.utils.heartbeat import Heartbeat, RankFailure, assert_peers_alive
+
+    hb = Heartbeat(hb_dir, rank)
+    t = torch.ones(4)
+    dist.all_reduce(t)  # step 1 works
+    hb.beat(1)
+    dist.barrier()
+    if rank == 1:
+        return  # "dies" here
+    time.sleep(1.5)
+    hb.beat(2)
+    with pytest.raises(RankFailure):
+        assert_peers_alive(hb_dir, world, max_age_s=1.0)
+
+
+@pytest.mark.distributed
+def test_survivor_detects_lost_peer_before_next_collective(tmp_path):
+    run_distributed(_lost_peer_worker, 2, str(tmp_path))
+
+
+def _timeout_worker(rank, world, init_file):
+    import torch.distributed as dist
+
+    group = dist.new_group(ranks=[0, 1], timeout=datetime.timedelta(seconds=2))
+    if rank == 1:
+        time.sleep(6)  # never joins the collective within the limit
+        return
+    with pytest.raises(Exception):
+        t = torch.ones(2)
+        dist.all_reduce(t, group=group)
+        dist.barrier(group=group)
+
+
+@pytest.mark.distributed
+def test_short_group_timeout_ends_a_collective_with_an_error(tmp_path):
+    run_distributed(_timeout_worker, 2, str(tmp_path))
+
+
+def _raising_worker(rank, world):
+    if rank == 1:
+        raise RuntimeError("injected host-side failure")
+    time.sleep(0.2)
+
+
+@pytest.mark.distributed
+def test_a_raising_rank_is_reported_by_the_launcher():
+    with pytest.raises(AssertionError, match="injected host-side failure"):
+        run_distributed(_raising_worker, 2)
+
+
+# ------------------------------------------------------------------ checkpoint / resume
+def _steps(model, step_fn, opt, cfg, seeds):
+    return [step_fn.train_step(model, random_batch(cfg, s), opt)["train/ce_loss"].value for s in seeds]
+
+
+def test_resume_reproduces_the_uninterrupted_run(tmp_path):
+    from nanotitan_b200.models.model import NanoTitanModel
+    from nanotitan_b200.parallel import PipelineParallel
+    from nanotitan_b200.parallel.reducer import ReducerV1
+    from nanotitan_b200.utils import seed_everything
+    from nanotitan_b200.utils.checkpoint import latest_checkpoint, load_checkpoint, save_checkpoint
+
+    cfg = tiny_app_cfg()
+
+    def build():
+        seed_everything(9)
+        model = NanoTitanModel(cfg.model, full_spec(cfg.model))
+        reducers = {k: ReducerV1(v, 1, None, 1) for k, v in model.parameter_sync_groups().items()}
+        dims = fake_dims(num_experts=4)
+        return model, PipelineParallel(cfg, dims, reducers), torch.optim.AdamW(model.parameters(), lr=1e-2, weight_decay=0.1), dims
+
+    model, step_fn, opt, dims = build()
+    straight = _steps(model, step_fn, opt, cfg, range(6))
+
+    model, step_fn, opt, dims = build()
+    first = _steps(model, step_fn, opt, cfg, range(3))
+    save_checkpoint(tmp_path, 3, 0, model, opt, dims, cfg)
+    (tmp_path / "step_00000009").mkdir()  # a save that never finished (no manifest) is ignored
+    model, step_fn, opt, dims = build()  # "restart"
+    found = latest_checkpoint(tmp_path)
+    assert found.name == "step_00000003"
+    assert load_checkpoint(found, model, opt, dims)["step"] == 3
+    resumed = _steps(model, step_fn, opt, cfg, range(3, 6))
+    assert first + resumed == straight  # bitwise
+
+
+# ------------------------------------------------------------------ device-side bounded wait
+@pytest.mark.gpu
+def test_device_wait_runs_out_and_reports_status():
+    from nanotitan_b200.ops.ext import get_ext
+
+    ext = get_ext()
+    ext.read_status(True)
+    assert ext.bounded_wait_probe(50.0) == 64  # every thread gave up, nobody hung
+    code, kernel, detail, count = ext.read_status(True)
+    assert (code, kernel) == (1, 7) and count >= 1
+    # the context is intact and later kernels run (the status word was cleared by the read)
+    x = torch.randn(256, 64, device="cuda").bfloat16()
+    w = torch.randn(64, 64, device="cuda").bfloat16()
+    from nanotitan_b200.ops import native
+
+    y = torch.empty(256, 64, device="cuda", dtype=torch.bfloat16)
+    native.gemm_tc(x, False, [w], False, [y])
+    torch.testing.assert_close(y.float(), x.float() @ w.float().t(), rtol=2e-2, atol=0.3)
+    assert ext.read_status(True)[0] == 0
+
+
+@pytest.mark.gpu
+def test_recorded_failure_turns_later_kernels_into_noops_until_cleared():
+    from nanotitan_b200.ops import native
+    from nanotitan_b200.ops.ext import get_ext
+
+    ext = get_ext()
+    ext.read_status(True)
+    ext.bounded_wait_probe(20.0)
+    x = torch.randn(128, 64, device="cuda").bfloat16()
+    y = torch.full((128, 64), 7.0, device="cuda", dtype=torch.bfloat16)
+    native.gemm_tc(x, False, [x[:64].contiguous()], False, [y])  # skipped: status word is set
+    assert (y == 7.0).all()
+    assert ext.read_status(True)[0] == 1
+    native.gemm_tc(x, False, [x[:64].contiguous()], False, [y])
+    assert not (y == 7.0).all()
