@@ -497,19 +497,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
       } else {
-        // kEpiSwigluBwd: accumulator = dH tile; R = GV [rows, 2N]; C[0] = dGV [rows, 2N]
+        // kEpiSwigluBwd: accumulator = dH tile; R = GV [rows, 2N]; C[0] = dGV [rows, 2N].
+        // The gate / value rows of chunk c+1 are requested before chunk c is processed, so their
+        // memory latency overlaps the TMEM read and the math instead of stalling every chunk.
+        const uint16_t* gv_row = reinterpret_cast<const uint16_t*>(args.R) + row * args.ldr;
+        const bool fast = row_ok && (reinterpret_cast<uintptr_t>(gv_row) & 15u) == 0 && (args.N % 8) == 0;
+        uint4 gq[4], uq[4];
+        auto fetch = [&](int col) {
+          if (fast && col + 32 <= args.N) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              gq[v] = __ldg(reinterpret_cast<const uint4*>(gv_row + col) + v);
+              uq[v] = __ldg(reinterpret_cast<const uint4*>(gv_row + args.N + col) + v);
+            }
+          }
+        };
+        fetch(ti.n0);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           const int col = ti.n0 + c0;
           if (col >= args.N) break;
           uint32_t r[32];
           tmem_ld_32x32(t_addr + c0, r);
-          tmem_ld_wait();
-          if (row_ok) {
-            const int valid = min(32, args.N - col);
-            float g[32], u[32], dg[32], du[32];
+          float g[32], u[32];
+          const int valid = min(32, args.N - col);
+          if (fast && valid == 32) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              unpack2(gq[v].x, args.dtype, g[8 * v + 0], g[8 * v + 1]); unpack2(gq[v].y, args.dtype, g[8 * v + 2], g[8 * v + 3]);
+              unpack2(gq[v].z, args.dtype, g[8 * v + 4], g[8 * v + 5]); unpack2(gq[v].w, args.dtype, g[8 * v + 6], g[8 * v + 7]);
+              unpack2(uq[v].x, args.dtype, u[8 * v + 0], u[8 * v + 1]); unpack2(uq[v].y, args.dtype, u[8 * v + 2], u[8 * v + 3]);
+              unpack2(uq[v].z, args.dtype, u[8 * v + 4], u[8 * v + 5]); unpack2(uq[v].w, args.dtype, u[8 * v + 6], u[8 * v + 7]);
+            }
+          } else if (row_ok) {
             load_row32(args.R, row * args.ldr + col, valid, args.dtype, g);
             load_row32(args.R, row * args.ldr + args.N + col, valid, args.dtype, u);
+          }
+          if (c0 + 32 < BN) fetch(col + 32);  // next chunk's rows are in flight during this chunk's math
+          tmem_ld_wait();
+          if (row_ok) {
+            float dg[32], du[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float dh = __uint_as_float(r[i]);

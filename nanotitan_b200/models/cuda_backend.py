@@ -31,7 +31,20 @@ class CUDAMoEBackend:
         if not flat.is_cuda:
             raise RuntimeError(f"moe_backend='cuda' needs GPU tensors (got {flat.device})")
         res = None if residual is None else residual.reshape(-1, d_model)
-        if self.spec.ep_size > 1:
+        if self.cfg.num_experts == 1 and self.spec.ep_size == 1:
+            # One expert: routing is the identity (gate 1, every token in place), so the layer is
+            # the dense SwiGLU FFN with the residual folded into the down-projection.  The router
+            # gets no gradient signal (softmax over one logit), exactly as in the general path.
+            from nanotitan_b200.ops import native
+
+            tokens = flat.shape[0]
+            offsets = native.whole_segment(tokens, flat.device)
+            with nvtx_range("moe/expert_compute"):
+                out = native.swiglu_experts(flat, self.experts.W_gate, self.experts.W_val, self.experts.W_out, offsets, res)
+            counts = torch.full((1,), tokens * self.cfg.top_k, dtype=torch.int32, device=flat.device)
+            # keeps the router weight in the graph with an exactly-zero gradient, as softmax over one logit gives
+            probs_mean = torch.ones(1, dtype=torch.float32, device=flat.device) + 0.0 * self.router.weight.float().sum()
+        elif self.spec.ep_size > 1:
             from nanotitan_b200.parallel.ep import expert_parallel_moe
 
             out, counts, probs_mean = expert_parallel_moe(self, flat, res)

@@ -355,15 +355,16 @@ class _SwigluExperts(torch.autograd.Function):
     stacked gate|value reduction, and the two weight-gradient GEMMs over ragged segments)."""
 
     @staticmethod
-    def forward(ctx, x, w_gate, w_val, w_out, offsets):
+    def forward(ctx, x, w_gate, w_val, w_out, offsets, residual):
         rows, f, d = x.shape[0], w_gate.shape[2], w_out.shape[2]
         gv = torch.empty(rows, 2 * f, dtype=x.dtype, device=x.device)
         h = torch.empty(rows, f, dtype=x.dtype, device=x.device)
         gemm_tc(x, False, [w_gate, w_val], True, [gv], b_split=B_DUAL, mode=GROUPED_M, offsets=offsets,
                 epilogue=EPI_SWIGLU_FWD, aux_out=h)
         y = torch.empty(rows, d, dtype=x.dtype, device=x.device)
-        gemm_tc(h, False, [w_out], True, [y], mode=GROUPED_M, offsets=offsets)
+        gemm_tc(h, False, [w_out], True, [y], mode=GROUPED_M, offsets=offsets, aux=residual)  # + residual in the epilogue
         ctx.save_for_backward(x, w_gate, w_val, w_out, offsets, gv, h)
+        ctx.has_res = residual is not None
         return y
 
     @staticmethod
@@ -380,17 +381,22 @@ class _SwigluExperts(torch.autograd.Function):
         gemm_tc(h, True, [dy], True, [d_out], mode=GROUPED_K, offsets=offsets)
         d_gate, d_val = torch.empty_like(w_gate), torch.empty_like(w_val)
         gemm_tc(x, True, [dgv], True, [d_gate, d_val], mode=GROUPED_K, offsets=offsets)
-        return dx, d_gate, d_val, d_out, None
+        return dx, d_gate, d_val, d_out, None, (dy if ctx.has_res else None)
 
 
-def swiglu_experts(x, w_gate, w_val, w_out, offsets):
-    offsets = offsets.to(torch.int32)
+def swiglu_experts(x, w_gate, w_val, w_out, offsets, residual=None):
+    """Expert SwiGLU FFN over expert-major rows; `residual` ([rows, d], row-aligned with x) is added
+    in the down-projection's epilogue."""
+    if offsets.dtype != torch.int32:
+        offsets = offsets.to(torch.int32)
     f = w_gate.shape[2]
     if tc_ok(x, w_gate, w_val, w_out) and f % 64 == 0 and w_gate.shape[0] <= 256:
-        return _SwigluExperts.apply(x.contiguous(), w_gate, w_val, w_out, offsets.contiguous())
+        res = None if residual is None else residual.contiguous()
+        return _SwigluExperts.apply(x.contiguous(), w_gate, w_val, w_out, offsets.contiguous(), res)
     gate = grouped_gemm(x, w_gate, offsets)
     val = grouped_gemm(x, w_val, offsets)
-    return grouped_gemm(torch.nn.functional.silu(gate) * val, w_out, offsets)
+    out = grouped_gemm(torch.nn.functional.silu(gate) * val, w_out, offsets)
+    return out if residual is None else out + residual
 
 
 def default_scale(d_head: int) -> float:
