@@ -35,6 +35,18 @@ def gemm_tc(a, a_mn, bs, b_mn, cs, *, b_split=B_ONE, mode=DENSE, offsets=None, e
                       aux, aux_out, force_bn)
 
 
+def grad_buffer(w: torch.Tensor) -> torch.Tensor:
+    """Where to write w's gradient: its slot in the data-parallel gradient bucket when this is the
+    step's first gradient for w (autograd then adopts the tensor as `w.grad` without a copy or an
+    add), else a fresh tensor."""
+    sink = getattr(w, "_nt_grad_sink", None)
+    if sink is not None and w.grad is None:
+        out = sink()
+        if out.dtype == w.dtype and out.shape == w.shape:
+            return out
+    return torch.empty_like(w)
+
+
 def _rows(t: torch.Tensor) -> torch.Tensor:
     """2-D row-major view/copy of the leading dims."""
     t2 = t.reshape(-1, t.shape[-1])
@@ -66,7 +78,7 @@ class _Linear(torch.autograd.Function):
             gemm_tc(dy2, False, [w], False, [dx])  # w as [N_out = in, K = out]: K-major
             dx = dx.view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
-            dw = torch.empty_like(w)
+            dw = grad_buffer(w)
             wgrad(x2, dy2, [dw])  # x^T dy: both operands MN-major, split over the token dim
         return dx, dw, (dy if ctx.has_res else None)
 
@@ -109,7 +121,7 @@ class _QKVProjection(torch.autograd.Function):
         d2 = _rows(dqkv)
         dx = torch.empty_like(x2)
         gemm_tc(d2, False, [wq, wk, wv], False, [dx], b_split=B_SPLIT_K)
-        dws = [torch.empty_like(w) for w in (wq, wk, wv)]
+        dws = [grad_buffer(w) for w in (wq, wk, wv)]
         wgrad(x2, d2, dws)
         return dx.view(ctx.x_shape), dws[0], dws[1], dws[2]
 
@@ -207,13 +219,13 @@ class _LinearCrossEntropy(torch.autograd.Function):
         gemm_tc(view, False, [w], True, [dx])  # reduction over V: w [V, d] is MN-major here
         dw = torch.empty_like(w)
         gemm_tc(view, True, [x], True, [dw])  # dlogits^T x
-        ctx.save_for_backward(dx, dw)
+        ctx.save_for_backward(dx, dw, w)
         return loss
 
     @staticmethod
     def backward(ctx, g):
-        dx, dw = ctx.saved_tensors
-        return dx * g.to(dx.dtype), dw * g.to(dw.dtype), None
+        dx, dw, w = ctx.saved_tensors
+        return dx * g.to(dx.dtype), torch.mul(dw, g.to(dw.dtype), out=grad_buffer(w)), None
 
 
 def linear_cross_entropy(x, w_unembed, targets):
@@ -377,9 +389,9 @@ class _SwigluExperts(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = torch.empty_like(x)
             gemm_tc(dgv, False, [w_gate, w_val], False, [dx], b_split=B_SPLIT_K, mode=GROUPED_M, offsets=offsets)
-        d_out = torch.empty_like(w_out)
+        d_out = grad_buffer(w_out)
         gemm_tc(h, True, [dy], True, [d_out], mode=GROUPED_K, offsets=offsets)
-        d_gate, d_val = torch.empty_like(w_gate), torch.empty_like(w_val)
+        d_gate, d_val = grad_buffer(w_gate), grad_buffer(w_val)
         gemm_tc(x, True, [dgv], True, [d_gate, d_val], mode=GROUPED_K, offsets=offsets)
         return dx, d_gate, d_val, d_out, None, (dy if ctx.has_res else None)
 

@@ -92,8 +92,9 @@ class PipelineParallel:
 
     def _zero_grad(self, optimizer) -> None:
         owned = {id(p) for r in self.reducers.values() for p in r.params}
+        lazy = self.device.type == "cuda"  # native kernels write first gradients into their bucket slots
         for r in self.reducers.values():
-            r.zero_grad()
+            r.zero_grad(lazy=lazy)
         for group in optimizer.param_groups:
             for p in group["params"]:
                 if id(p) not in owned:

@@ -100,9 +100,23 @@ class ReducerV1:
     def attach_grad_views(self) -> None:
         for p in self.params:
             p.grad = self.grad_view(p)
+            # Kernels that produce this parameter's gradient may ask for its bucket slot and write
+            # there directly (see `zero_grad(lazy=True)`).
+            p._nt_grad_sink = (lambda q=p: self.grad_view(q))
 
-    def zero_grad(self) -> None:
-        """One memset per bucket; re-attaches views an outside `zero_grad(set_to_none)` dropped."""
+    def zero_grad(self, lazy: bool = False) -> None:
+        """Eager (default): one memset per bucket, every `param.grad` is its zeroed bucket view.
+
+        Lazy: gradients are dropped (`param.grad = None`) and nothing is written.  The first
+        gradient of a step is then *produced in place*: weight-gradient kernels write into the
+        parameter's bucket slot (`_nt_grad_sink`) and autograd adopts that tensor as `.grad`, so the
+        step has neither a zero-fill nor an add pass for those parameters; gradients that arrive as
+        ordinary tensors are copied into their slot by the hook, and parameters that never get one
+        are zero-filled by `prepare_missing_grad`."""
+        if lazy:
+            for p in self.params:
+                p.grad = None
+            return
         for b in self.buckets:
             b.buffer.zero_()
         for p in self.params:
@@ -147,6 +161,7 @@ class ReducerV1:
             if p not in self.ready_for_sync:
                 if p.grad is None:
                     p.grad = self.grad_view(p)
+                    p.grad.zero_()  # the slot may hold last step's values (lazy zero_grad)
                 self.reduce_grad(p)
 
     def finalize_backward(self) -> None:
