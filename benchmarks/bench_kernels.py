@@ -99,11 +99,14 @@ def bench_gemm(iters):
     report("swiglu experts bwd T30720 d512 f2048", ms, flops=12.0 * T * 512 * 2048)
 
 
+ATTN_SHAPES = [(40, 768, 16, 32), (4, 1024, 16, 64), (16, 2048, 8, 64)]
+
+
 def bench_attn(iters):
     ext = get_ext()
     if not hasattr(ext, "flash_fwd"):
         return
-    for B, S, H, Dh in ((40, 768, 16, 32), (4, 1024, 16, 64), (16, 2048, 8, 64)):
+    for B, S, H, Dh in ATTN_SHAPES:
         q, k, v = (rnd(B, S, H, Dh) for _ in range(3))
         scale = Dh**-0.5
         flops = 2.0 * B * H * S * S * Dh  # causal: half of 4*S*S*Dh
@@ -184,10 +187,13 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shape", default="30720,512,2048", help="M,N,K of --only single")
     ap.add_argument("--b-mn", type=int, default=1, help="--only single: 1 = B stored [K,N]")
+    ap.add_argument("--attn-shape", default="", help="B,S,H,Dh: run --only attn on this one shape")
     ap.add_argument("--only", default="gemm,attn,moe,norm,ce,adamw")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
     table = {"gemm": bench_gemm, "attn": bench_attn, "moe": bench_moe, "norm": bench_norm, "ce": bench_ce, "adamw": bench_adamw}
+    if args.attn_shape:
+        ATTN_SHAPES[:] = [tuple(int(v) for v in args.attn_shape.split(","))]
     for key in args.only.split(","):
         if key.strip() == "single":
             bench_single(args.iters, tuple(int(v) for v in args.shape.split(",")), bool(args.b_mn))

@@ -29,6 +29,7 @@
 #include "sm100.cuh"
 #include "tma_desc.h"
 
+#include <cstdlib>
 #include <type_traits>
 
 namespace nt {
@@ -174,7 +175,7 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
     for (int s = 0; s < 2; ++s) { mbar_init(&c_full[s], 1); mbar_init(&c_empty[s], 1); }
     mbar_init(t_full, 1);
     mbar_init(t_full_b, 1);
-    mbar_init(e_full, 128);
+    mbar_init(e_full, 4);  // one arrival per softmax warp
     mbar_init(e_empty, 1);
     mbar_init(acc_full, 1);
     *abort_flag = 0u;
@@ -386,7 +387,8 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
           write_e_chunk(e1, r, 32, phi, args.dtype);
         }
         fence_proxy_async_smem();
-        mbar_arrive(e_full);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(e_full);
         l_run = l_run * alpha + l_add;
         m_run = m_new;
         alpha_prev = alpha;
@@ -394,7 +396,7 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
       if (ok && n_iter > 0) ok = fold_pv(n_iter - 1);
     }
     int stage = 0;
-    for (int it = 0; it < n_iter && ok && MODE != kFwd; ++it) {
+    for (int it = 0; it < n_iter && MODE != kFwd; ++it) {  // runs to the end even after an abandoned wait: see named_sync below
       const int c0 = (c_begin + it) * BC;  // first streamed index (key for fwd/dq, query for dkv)
       if (MODE == kDkv) {
         // stage the streamed queries' lse / dsum in shared memory (values past S are neutral)
@@ -406,10 +408,11 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
         }
         named_sync_softmax();
       }
-      if (!mbar_wait(t_full, it & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 300)) { ok = false; break; }
+      if (!ok) { if (++stage == C::STAGES) stage = 0; continue; }
+      if (!mbar_wait(t_full, it & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 300)) { ok = false; continue; }
       tc_fence_after();
       if (it > 0) {
-        if (!mbar_wait(e_empty, (it - 1) & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 310)) { ok = false; break; }
+        if (!mbar_wait(e_empty, (it - 1) & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 310)) { ok = false; continue; }
       }
       {
         const float* vl = vec + stage * 2 * BC;
@@ -453,7 +456,8 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
         if (need_mask) process(std::true_type{}); else process(std::false_type{});
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(e_full);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(e_full);
       }
       if (++stage == C::STAGES) stage = 0;
     }
