@@ -3,8 +3,11 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <cstdlib>
+
 #include "cuda_check.h"
 #include "gemm_tc.cuh"
+#include "gemm_tc2.cuh"
 #include "ops.h"
 #include "tma_desc.h"
 
@@ -61,6 +64,25 @@ void launch(const CUtensorMap& tA, const CUtensorMap (&tB)[3], const Args& args,
   const int grid = std::max(1, std::min(tiles, sms));
   kernel<<<grid, gemm::NUM_THREADS, S::TOTAL, stream>>>(tA, tB[0], tB[1], tB[2], args);
   NT_KERNEL_CHECK();
+}
+
+template <int EPI>
+void launch_pair(const CUtensorMap& tA, const CUtensorMap (&tB)[3], const Args& args, int tiles, cudaStream_t stream) {
+  auto kernel = gemm::gemm_tc_pair_kernel<EPI>;
+  static bool configured = false;
+  if (!configured) {
+    NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::PAIR_SMEM));
+    configured = true;
+  }
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount & ~1;
+  const int grid = std::max(2, std::min(2 * tiles, sms));
+  kernel<<<grid, gemm::NUM_THREADS, gemm::PAIR_SMEM, stream>>>(tA, tB[0], tB[1], tB[2], args);  // clusters of 2 (compile-time attribute)
+  NT_KERNEL_CHECK();
+}
+
+bool pair_kernels_enabled() {
+  static const bool v = [] { const char* e = std::getenv("NT_GEMM_PAIR"); return e == nullptr || e[0] != '0'; }();
+  return v;
 }
 
 // 256-wide tiles move 1.5x fewer bytes per flop through shared memory than 128-wide ones, and
@@ -264,9 +286,31 @@ void gemm_tc(const at::Tensor& A, bool a_mn, const std::vector<at::Tensor>& Bs, 
   else if (mode == gemm::kGroupedM) m_tiles = (args.M + gemm::BM - 1) / gemm::BM + args.G;  // upper bound
   else m_tiles = args.G * ((args.M + gemm::BM - 1) / gemm::BM);
 
+  // ---- CTA-pair kernel (256 x 256 tiles, cta_group::2) for the non-ragged-reduction shapes
+  const bool pair_ok = mode != gemm::kGroupedK && args.N > 128 && args.M >= 256 && ndst == 1 &&
+                       (b_split != gemm::kBSplitN || args.b_split_size % gemm::PAIR_BN == 0);
+  const bool use_pair = force_bn == 512 || (force_bn == 0 && pair_ok && pair_kernels_enabled());
+  if (use_pair) {
+    TORCH_CHECK(pair_ok, "gemm_tc: this problem cannot run on the CTA-pair kernel");
+    const int pm = mode == gemm::kDense ? (args.M + gemm::PAIR_BM - 1) / gemm::PAIR_BM
+                                         : (args.M + gemm::PAIR_BM - 1) / gemm::PAIR_BM + args.G;
+    const int ptn = epilogue == gemm::kEpiSwigluFwd ? gemm::PAIR_BN / 2 : gemm::PAIR_BN;
+    const int ptiles = pm * ((args.N + ptn - 1) / ptn);
+    args.k_splits = 1;
+    const CUtensorMap ptA = map_a(A, a_mn);
+    CUtensorMap ptB[3];
+    for (int i = 0; i < 3; ++i) ptB[i] = map_b(Bs[std::min(i, nsrc - 1)], b_mn, gemm::PAIR_BN / 2);
+    cudaStream_t pstream = at::cuda::getCurrentCUDAStream();
+    if (epilogue == gemm::kEpiSwigluFwd) launch_pair<gemm::kEpiSwigluFwd>(ptA, ptB, args, ptiles, pstream);
+    else if (epilogue == gemm::kEpiSwigluBwd) launch_pair<gemm::kEpiSwigluBwd>(ptA, ptB, args, ptiles, pstream);
+    else launch_pair<gemm::kEpiStore>(ptA, ptB, args, ptiles, pstream);
+    return;
+  }
+
   int bn = epilogue == gemm::kEpiSwigluFwd ? 256 : pick_bn(m_tiles, args.N, sms);
   if (mode == gemm::kGroupedK && args.N >= 256) bn = 256;  // split-K fills the GPU; keep the wide tile
   if (force_bn > 0) bn = static_cast<int>(force_bn);
+  if (force_bn < 0) bn = epilogue == gemm::kEpiSwigluFwd ? 256 : pick_bn(m_tiles, args.N, sms);  // -1: one-CTA kernel, automatic tile
   TORCH_CHECK(bn == 64 || bn == 128 || bn == 256, "BN must be 64, 128 or 256");
   if (b_split == gemm::kBSplitN) {
     while (bn > 64 && args.b_split_size % bn != 0) bn /= 2;

@@ -229,6 +229,147 @@ __device__ __forceinline__ void store_row32(void* base, long long elem_off, int 
   }
 }
 
+// Drains one accumulator tile (this warp's 32 TMEM lanes = 32 rows) through the epilogue EPI.
+// `t_addr`: TMEM address of the tile's first column in this warp's lanes; `row`: global row of
+// this thread; `row_ok`: the row exists; `have_acc`: the tile had at least one reduction step.
+template <int BN, int EPI>
+__device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, uint32_t t_addr, bool row_ok, bool have_acc, long long row) {
+  using namespace sm100;
+  if constexpr (EPI == kEpiStore) {
+    const long long grp_off = (args.mode == kGroupedK) ? static_cast<long long>(ti.g) * args.c_group_stride : 0;
+    const bool partial = args.mode == kGroupedK && args.k_splits > 1;
+    float* ws_tile = partial ? args.ws + (static_cast<long long>(ti.split) * args.G + ti.g) * args.M * args.N : nullptr;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      const int col = ti.n0 + c0;
+      if (col >= args.N) break;  // uniform across the warp
+      float v[32];
+      if (have_acc) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+      }
+      if (row_ok && partial) {
+        store_row32(ws_tile, row * args.N + col, min(32, args.N - col), args.dtype, true, v);
+      } else if (row_ok) {
+        const int valid = min(32, args.N - col);
+        if (args.R != nullptr) {
+          float rr[32];
+          load_row32(args.R, row * args.ldr + col, valid, args.dtype, rr);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] += rr[i];
+        }
+        void* dst = args.C[0];
+        int dcol = col;
+        if (args.c_split_size > 0) {
+          const int d = col / args.c_split_size;
+          dst = args.C[d];
+          dcol = col - d * args.c_split_size;
+        }
+        const long long off = grp_off + row * args.ldc + dcol;
+        if (args.accumulate) {
+          if (args.out_f32) {
+            const float* p = reinterpret_cast<const float*>(dst) + off;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < valid) v[i] += p[i];
+          } else {
+            float old[32];
+            load_row32(dst, off, valid, args.dtype, old);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += old[i];
+          }
+        }
+        store_row32(dst, off, valid, args.dtype, args.out_f32 != 0, v);
+      }
+    }
+  } else if constexpr (EPI == kEpiSwigluFwd) {
+    // accumulator columns [0, BN/2) = gate, [BN/2, BN) = value, for output columns n0 .. n0+BN/2
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+      const int col = ti.n0 + c0;
+      if (col >= args.N) break;
+      uint32_t rg[32], rv[32];
+      tmem_ld_32x32(t_addr + c0, rg);
+      tmem_ld_32x32(t_addr + BN / 2 + c0, rv);
+      tmem_ld_wait();
+      if (row_ok) {
+        const int valid = min(32, args.N - col);
+        float g[32], u[32], h[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          g[i] = __uint_as_float(rg[i]);
+          u[i] = __uint_as_float(rv[i]);
+        }
+        // round gate / value to the storage dtype first so backward sees what forward used
+        store_row32(args.C[0], row * args.ldc + col, valid, args.dtype, false, g);
+        store_row32(args.C[0], row * args.ldc + args.N + col, valid, args.dtype, false, u);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) h[i] = silu_f(g[i]) * u[i];
+        store_row32(args.C2, row * args.ldc2 + col, valid, args.dtype, false, h);
+      }
+    }
+  } else {
+    // kEpiSwigluBwd: accumulator = dH tile; R = GV [rows, 2N]; C[0] = dGV [rows, 2N].
+    // The gate / value rows of chunk c+1 are requested before chunk c is processed, so their
+    // memory latency overlaps the TMEM read and the math instead of stalling every chunk.
+    const uint16_t* gv_row = reinterpret_cast<const uint16_t*>(args.R) + row * args.ldr;
+    const bool fast = row_ok && (reinterpret_cast<uintptr_t>(gv_row) & 15u) == 0 && (args.N % 8) == 0;
+    uint4 gq[4], uq[4];
+    auto fetch = [&](int col) {
+      if (fast && col + 32 <= args.N) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          gq[v] = __ldg(reinterpret_cast<const uint4*>(gv_row + col) + v);
+          uq[v] = __ldg(reinterpret_cast<const uint4*>(gv_row + args.N + col) + v);
+        }
+      }
+    };
+    fetch(ti.n0);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      const int col = ti.n0 + c0;
+      if (col >= args.N) break;
+      uint32_t r[32];
+      tmem_ld_32x32(t_addr + c0, r);
+      float g[32], u[32];
+      const int valid = min(32, args.N - col);
+      if (fast && valid == 32) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          unpack2(gq[v].x, args.dtype, g[8 * v + 0], g[8 * v + 1]); unpack2(gq[v].y, args.dtype, g[8 * v + 2], g[8 * v + 3]);
+          unpack2(gq[v].z, args.dtype, g[8 * v + 4], g[8 * v + 5]); unpack2(gq[v].w, args.dtype, g[8 * v + 6], g[8 * v + 7]);
+          unpack2(uq[v].x, args.dtype, u[8 * v + 0], u[8 * v + 1]); unpack2(uq[v].y, args.dtype, u[8 * v + 2], u[8 * v + 3]);
+          unpack2(uq[v].z, args.dtype, u[8 * v + 4], u[8 * v + 5]); unpack2(uq[v].w, args.dtype, u[8 * v + 6], u[8 * v + 7]);
+        }
+      } else if (row_ok) {
+        load_row32(args.R, row * args.ldr + col, valid, args.dtype, g);
+        load_row32(args.R, row * args.ldr + args.N + col, valid, args.dtype, u);
+      }
+      if (c0 + 32 < BN) fetch(col + 32);  // next chunk's rows are in flight during this chunk's math
+      tmem_ld_wait();
+      if (row_ok) {
+        float dg[32], du[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float dh = __uint_as_float(r[i]);
+          const float sig = 1.f / (1.f + __expf(-g[i]));
+          const float sl = g[i] * sig;
+          dg[i] = dh * u[i] * (sig * (1.f + g[i] * (1.f - sig)));
+          du[i] = dh * sl;
+        }
+        store_row32(args.C[0], row * args.ldc + col, valid, args.dtype, false, dg);
+        store_row32(args.C[0], row * args.ldc + args.N + col, valid, args.dtype, false, du);
+      }
+    }
+  }
+}
+
 template <int BN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
@@ -417,139 +558,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const bool have_acc = ti.k_chunks > 0;
       const long long row = static_cast<long long>(ti.m0) + row_in_tile;
 
-      if constexpr (EPI == kEpiStore) {
-        const long long grp_off = (args.mode == kGroupedK) ? static_cast<long long>(ti.g) * args.c_group_stride : 0;
-        const bool partial = args.mode == kGroupedK && args.k_splits > 1;
-        float* ws_tile = partial ? args.ws + (static_cast<long long>(ti.split) * args.G + ti.g) * args.M * args.N : nullptr;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          const int col = ti.n0 + c0;
-          if (col >= args.N) break;  // uniform across the warp
-          float v[32];
-          if (have_acc) {
-            uint32_t r[32];
-            tmem_ld_32x32(t_addr + c0, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0.f;
-          }
-          if (row_ok && partial) {
-            store_row32(ws_tile, row * args.N + col, min(32, args.N - col), args.dtype, true, v);
-          } else if (row_ok) {
-            const int valid = min(32, args.N - col);
-            if (args.R != nullptr) {
-              float rr[32];
-              load_row32(args.R, row * args.ldr + col, valid, args.dtype, rr);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] += rr[i];
-            }
-            void* dst = args.C[0];
-            int dcol = col;
-            if (args.c_split_size > 0) {
-              const int d = col / args.c_split_size;
-              dst = args.C[d];
-              dcol = col - d * args.c_split_size;
-            }
-            const long long off = grp_off + row * args.ldc + dcol;
-            if (args.accumulate) {
-              if (args.out_f32) {
-                const float* p = reinterpret_cast<const float*>(dst) + off;
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  if (i < valid) v[i] += p[i];
-              } else {
-                float old[32];
-                load_row32(dst, off, valid, args.dtype, old);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] += old[i];
-              }
-            }
-            store_row32(dst, off, valid, args.dtype, args.out_f32 != 0, v);
-          }
-        }
-      } else if constexpr (EPI == kEpiSwigluFwd) {
-        // accumulator columns [0, BN/2) = gate, [BN/2, BN) = value, for output columns n0 .. n0+BN/2
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN / 2; c0 += 32) {
-          const int col = ti.n0 + c0;
-          if (col >= args.N) break;
-          uint32_t rg[32], rv[32];
-          tmem_ld_32x32(t_addr + c0, rg);
-          tmem_ld_32x32(t_addr + BN / 2 + c0, rv);
-          tmem_ld_wait();
-          if (row_ok) {
-            const int valid = min(32, args.N - col);
-            float g[32], u[32], h[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              g[i] = __uint_as_float(rg[i]);
-              u[i] = __uint_as_float(rv[i]);
-            }
-            // round gate / value to the storage dtype first so backward sees what forward used
-            store_row32(args.C[0], row * args.ldc + col, valid, args.dtype, false, g);
-            store_row32(args.C[0], row * args.ldc + args.N + col, valid, args.dtype, false, u);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) h[i] = silu_f(g[i]) * u[i];
-            store_row32(args.C2, row * args.ldc2 + col, valid, args.dtype, false, h);
-          }
-        }
-      } else {
-        // kEpiSwigluBwd: accumulator = dH tile; R = GV [rows, 2N]; C[0] = dGV [rows, 2N].
-        // The gate / value rows of chunk c+1 are requested before chunk c is processed, so their
-        // memory latency overlaps the TMEM read and the math instead of stalling every chunk.
-        const uint16_t* gv_row = reinterpret_cast<const uint16_t*>(args.R) + row * args.ldr;
-        const bool fast = row_ok && (reinterpret_cast<uintptr_t>(gv_row) & 15u) == 0 && (args.N % 8) == 0;
-        uint4 gq[4], uq[4];
-        auto fetch = [&](int col) {
-          if (fast && col + 32 <= args.N) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              gq[v] = __ldg(reinterpret_cast<const uint4*>(gv_row + col) + v);
-              uq[v] = __ldg(reinterpret_cast<const uint4*>(gv_row + args.N + col) + v);
-            }
-          }
-        };
-        fetch(ti.n0);
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          const int col = ti.n0 + c0;
-          if (col >= args.N) break;
-          uint32_t r[32];
-          tmem_ld_32x32(t_addr + c0, r);
-          float g[32], u[32];
-          const int valid = min(32, args.N - col);
-          if (fast && valid == 32) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              unpack2(gq[v].x, args.dtype, g[8 * v + 0], g[8 * v + 1]); unpack2(gq[v].y, args.dtype, g[8 * v + 2], g[8 * v + 3]);
-              unpack2(gq[v].z, args.dtype, g[8 * v + 4], g[8 * v + 5]); unpack2(gq[v].w, args.dtype, g[8 * v + 6], g[8 * v + 7]);
-              unpack2(uq[v].x, args.dtype, u[8 * v + 0], u[8 * v + 1]); unpack2(uq[v].y, args.dtype, u[8 * v + 2], u[8 * v + 3]);
-              unpack2(uq[v].z, args.dtype, u[8 * v + 4], u[8 * v + 5]); unpack2(uq[v].w, args.dtype, u[8 * v + 6], u[8 * v + 7]);
-            }
-          } else if (row_ok) {
-            load_row32(args.R, row * args.ldr + col, valid, args.dtype, g);
-            load_row32(args.R, row * args.ldr + args.N + col, valid, args.dtype, u);
-          }
-          if (c0 + 32 < BN) fetch(col + 32);  // next chunk's rows are in flight during this chunk's math
-          tmem_ld_wait();
-          if (row_ok) {
-            float dg[32], du[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float dh = __uint_as_float(r[i]);
-              const float sig = 1.f / (1.f + __expf(-g[i]));
-              const float sl = g[i] * sig;
-              dg[i] = dh * u[i] * (sig * (1.f + g[i] * (1.f - sig)));
-              du[i] = dh * sl;
-            }
-            store_row32(args.C[0], row * args.ldc + col, valid, args.dtype, false, dg);
-            store_row32(args.C[0], row * args.ldc + args.N + col, valid, args.dtype, false, du);
-          }
-        }
-      }
+      epilogue_rows<BN, EPI>(args, ti, t_addr, row_ok, have_acc, row);
       tc_fence_before();
       mbar_arrive(&tmem_empty[acc]);
       acc ^= 1;

@@ -187,3 +187,66 @@ def test_results_are_bitwise_reproducible():
         native.gemm_tc(a, False, [b], False, [c])
         outs.append(c)
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (1024, 512, 512), (777, 1001, 264), (3000, 264, 136)])
+def test_cta_pair_kernel_matches_reference(a_mn, b_mn, M, N, K):
+    """The cta_group::2 kernel (256 x 256 tiles over two CTAs) on full and ragged tiles."""
+    from nanotitan_b200.ops import native
+
+    torch.manual_seed(8)
+    pad = lambda n: (n + 7) // 8 * 8  # noqa: E731
+    a = _rand(M, K)
+    b = _rand(N, K, scale=0.1)
+    a_op = a.t().contiguous() if a_mn else a
+    if a_mn and M % 8:
+        a_op = torch.zeros(K, pad(M), device="cuda", dtype=torch.bfloat16)
+        a_op[:, :M] = a.t()
+        a_op = a_op[:, :M]
+    b_op = b
+    if b_mn:
+        b_op = torch.zeros(K, pad(N), device="cuda", dtype=torch.bfloat16)
+        b_op[:, :N] = b.t()
+        b_op = b_op[:, :N]
+    outs = []
+    for force in (512, -1):
+        c = torch.full((M, pad(N)), float("nan"), device="cuda", dtype=torch.bfloat16)[:, :N]
+        native.gemm_tc(a_op, a_mn, [b_op], b_mn, [c], force_bn=force)
+        outs.append(c)
+    _status_clean()
+    want = a.float() @ b.float().t()
+    torch.testing.assert_close(outs[0].float(), want, rtol=2e-2, atol=0.02 * K**0.5)
+    assert torch.equal(outs[0], outs[1])  # same products, same accumulation order
+
+
+def test_cta_pair_grouped_and_swiglu():
+    from nanotitan_b200.ops import native
+
+    torch.manual_seed(9)
+    counts = [300, 0, 513, 129]
+    E, d, f = len(counts), 128, 256
+    rows = sum(counts)
+    x = _rand(rows, d)
+    wg, wv = _rand(E, d, f, scale=0.1), _rand(E, d, f, scale=0.1)
+    off = _offsets(counts)
+    res = []
+    for force in (512, -1):
+        gv = torch.zeros(rows, 2 * f, device="cuda", dtype=torch.bfloat16)
+        h = torch.zeros(rows, f, device="cuda", dtype=torch.bfloat16)
+        native.gemm_tc(x, False, [wg, wv], True, [gv], b_split=native.B_DUAL, mode=native.GROUPED_M, offsets=off,
+                       epilogue=native.EPI_SWIGLU_FWD, aux_out=h, force_bn=force)
+        dgv = torch.zeros_like(gv)
+        torch.manual_seed(10)
+        dy = _rand(rows, d)
+        wo = _rand(E, f, d, scale=0.1)
+        native.gemm_tc(dy, False, [wo], False, [dgv], mode=native.GROUPED_M, offsets=off, epilogue=native.EPI_SWIGLU_BWD,
+                       aux=gv, force_bn=force)
+        dx = torch.zeros(rows, d, device="cuda", dtype=torch.bfloat16)
+        native.gemm_tc(dgv, False, [wg, wv], False, [dx], b_split=native.B_SPLIT_K, mode=native.GROUPED_M, offsets=off,
+                       force_bn=force)
+        res.append((gv, h, dgv, dx))
+    _status_clean()
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
+    assert res[0][1].abs().max() > 0 and res[0][3].abs().max() > 0
