@@ -81,7 +81,7 @@ void launch_pair(const CUtensorMap& tA, const CUtensorMap (&tB)[3], const Args& 
 }
 
 bool pair_kernels_enabled() {
-  static const bool v = [] { const char* e = std::getenv("NT_GEMM_PAIR"); return e == nullptr || e[0] != '0'; }();
+  static const bool v = [] { const char* e = std::getenv("NT_GEMM_PAIR"); return e != nullptr && e[0] == '1'; }();  // opt-in
   return v;
 }
 
