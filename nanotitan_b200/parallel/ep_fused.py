@@ -38,7 +38,7 @@ class FusedExchange:
         self.rank = dist.get_rank(group)
         self.E = num_experts
         self.E_loc = num_experts // self.ep
-        self.wait_ms = float(os.environ.get("NT_COMM_WAIT_MS", "20000"))
+        self.wait_ms = float(os.environ.get("NT_COMM_WAIT_MS", "60000"))
         self.blocks = int(os.environ.get("NT_EP_BLOCKS", "96"))
         self._handles = {}
         self.flags = self._alloc(FLAG_WORDS, torch.int32)

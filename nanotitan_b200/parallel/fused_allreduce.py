@@ -37,7 +37,7 @@ class BucketEngine:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.use_multicast = os.environ.get("NT_MULTIMEM", "1") != "0"
-        self.wait_ms = float(os.environ.get("NT_COMM_WAIT_MS", "20000"))
+        self.wait_ms = float(os.environ.get("NT_COMM_WAIT_MS", "60000"))
         self.blocks = int(os.environ.get("NT_ALLREDUCE_BLOCKS", "64"))
         self.stream = torch.cuda.Stream(device=device)
         self._handles: dict[int, object] = {}

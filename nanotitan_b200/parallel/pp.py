@@ -67,6 +67,21 @@ class PipelineParallel:
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
 
+    def _raise_on_device_failure(self) -> None:
+        """Bounded device-side waits record a status word instead of hanging; surface it here."""
+        if self.device.type != "cuda":
+            return
+        from nanotitan_b200.ops import ext
+
+        if not ext.have_ext():
+            return
+        code, kernel, detail, count = ext.get_ext().read_status(True)
+        if code != 0:
+            raise RuntimeError(
+                f"a device-side wait or check failed during this step (code={code}, kernel={kernel}, "
+                f"detail={detail}, events={count}); a peer rank is probably gone or stalled"
+            )
+
     def prepare_microbatch(self, x, y):
         n = self.cfg.runtime.num_microbatches
         assert x.shape[0] % n == 0
@@ -176,6 +191,7 @@ class PipelineParallel:
         else:
             ce_sum = aux_sum = 0.0
         self.synchronize_device()
+        self._raise_on_device_failure()
         step_time = clock.seconds("start", "end")
         metrics = {
             "train/ce_loss": ScalarMetric(ce_sum / n_mb, reduce="sum"),
