@@ -129,7 +129,8 @@ __device__ __forceinline__ void store_row(void* base, long long off, const float
 
 // tm0/tm1: resident tensors (box {Dh, 128, 1, 1}); tm2/tm3: streamed tensors (box {Dh, BC, 1, 1}).
 // Tensor maps are 4-D over (Dh, H, S, B) so a tile is addressed as (0, h, s0, b).
-template <int DH, int MODE>
+// DT: 0 = fp16, 1 = bf16 (compile-time so the pack / convert code has no per-element selects)
+template <int DH, int MODE, int DT>
 __global__ void __launch_bounds__(THREADS, 2)
 flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1,
              const __grid_constant__ CUtensorMap tm2, const __grid_constant__ CUtensorMap tm3, const Args args) {
@@ -213,8 +214,8 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    const uint32_t idesc_t = umma_idesc(args.dtype, BR, BC, 0, 0);
-    const uint32_t idesc_acc = umma_idesc(args.dtype, BR, DH, 0, 1);
+    const uint32_t idesc_t = umma_idesc(DT, BR, BC, 0, 0);
+    const uint32_t idesc_acc = umma_idesc(DT, BR, DH, 0, 1);
     const uint32_t ra = smem_u32(smem + C::OFF_R), rb = ra + C::R_TILE;
     const uint32_t e1 = smem_u32(smem + C::OFF_E), e2 = e1 + C::E_TILE;
     bool ok = mbar_wait(r_full, 0, abort_flag, args.status, kKernelAttnFwd + MODE, 200);
@@ -366,25 +367,34 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
             m_new = fmaxf(m_new, __uint_as_float(t[i]));
           }
         } else {
+          float m4[4] = {m_new, m_new, m_new, m_new};  // four independent chains instead of one of 64
 #pragma unroll
-          for (int i = 0; i < BC; ++i) m_new = fmaxf(m_new, __uint_as_float(t[i]));
+          for (int i = 0; i < BC; i += 4) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) m4[j] = fmaxf(m4[j], __uint_as_float(t[i + j]));
+          }
+          m_new = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         }
         const float alpha = exp2f((m_run - m_new) * sl2);  // first tile: m_run = -inf -> 0
         const float shift = m_new * sl2;
-        float l_add = 0.f;
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < BC; ++i) {
-          const float pi = exp2f(fmaf(__uint_as_float(t[i]), sl2, -shift));  // exp2(-inf) = 0 for masked entries
-          l_add += pi;
-          t[i] = __float_as_uint(pi);  // probabilities replace the scores in place
+        for (int i = 0; i < BC; i += 4) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float pi = exp2f(fmaf(__uint_as_float(t[i + j]), sl2, -shift));  // exp2(-inf) = 0 for masked entries
+            l4[j] += pi;
+            t[i + j] = __float_as_uint(pi);  // probabilities replace the scores in place
+          }
         }
+        const float l_add = (l4[0] + l4[1]) + (l4[2] + l4[3]);
         // the previous step's P.V finished long ago; folding it here keeps its latency off the loop
         if (it > 0 && !fold_pv(it - 1)) { ok = false; break; }
         {
           float (&plo)[32] = *reinterpret_cast<float (*)[32]>(&t[0]);
           float (&phi)[32] = *reinterpret_cast<float (*)[32]>(&t[32]);
-          write_e_chunk(e1, r, 0, plo, args.dtype);
-          write_e_chunk(e1, r, 32, phi, args.dtype);
+          write_e_chunk(e1, r, 0, plo, DT);
+          write_e_chunk(e1, r, 32, phi, DT);
         }
         fence_proxy_async_smem();
         __syncwarp();
@@ -446,10 +456,10 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
               ds[i] = p * (__uint_as_float(t2[i]) - dsum) * args.scale;
             }
             if (MODE == kDq) {
-              write_e_chunk(e1, r, cc, ds, args.dtype);
+              write_e_chunk(e1, r, cc, ds, DT);
             } else {
-              write_e_chunk(e1, r, cc, pv, args.dtype);
-              write_e_chunk(e2, r, cc, ds, args.dtype);
+              write_e_chunk(e1, r, cc, pv, DT);
+              write_e_chunk(e2, r, cc, ds, DT);
             }
           }
         };
@@ -474,7 +484,7 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
         const float inv = 1.f / l_run;
 #pragma unroll
         for (int i = 0; i < DH; ++i) o_acc[i] *= inv;
-        store_row<DH>(args.out0, off, o_acc, args.dtype);
+        store_row<DH>(args.out0, off, o_acc, DT);
         args.lse[bh * S + row_idx] = m_run * args.scale + logf(l_run);
       }
     }
@@ -499,7 +509,7 @@ flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CU
         if (ok && row_idx < S) {
           const long long off = static_cast<long long>(b) * args.o_sb + static_cast<long long>(row_idx) * args.o_ss +
                                 static_cast<long long>(h) * args.o_sh;
-          store_row<DH>(which == 0 ? args.out0 : args.out1, off, v, args.dtype);
+          store_row<DH>(which == 0 ? args.out0 : args.out1, off, v, DT);
         }
       }
     }
@@ -561,14 +571,15 @@ void check_bshd(const at::Tensor& t, const char* name) {
 template <int DH, int MODE>
 void launch(const CUtensorMap& m0, const CUtensorMap& m1, const CUtensorMap& m2, const CUtensorMap& m3, const Args& a, cudaStream_t stream) {
   using C = Cfg<DH, MODE>;
-  auto kernel = flash_kernel<DH, MODE>;
   static bool configured = false;
   if (!configured) {
-    NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
+    NT_CUDA_CHECK(cudaFuncSetAttribute(flash_kernel<DH, MODE, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
+    NT_CUDA_CHECK(cudaFuncSetAttribute(flash_kernel<DH, MODE, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
     configured = true;
   }
   dim3 grid((a.S + BR - 1) / BR, a.H, a.B);
-  kernel<<<grid, THREADS, C::TOTAL, stream>>>(m0, m1, m2, m3, a);
+  if (a.dtype == 1) flash_kernel<DH, MODE, 1><<<grid, THREADS, C::TOTAL, stream>>>(m0, m1, m2, m3, a);
+  else flash_kernel<DH, MODE, 0><<<grid, THREADS, C::TOTAL, stream>>>(m0, m1, m2, m3, a);
   NT_KERNEL_CHECK();
 }
 

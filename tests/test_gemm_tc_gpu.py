@@ -225,7 +225,7 @@ def test_cta_pair_grouped_and_swiglu():
 
     torch.manual_seed(9)
     counts = [300, 0, 513, 129]
-    E, d, f = len(counts), 128, 256
+    E, d, f = len(counts), 256, 384
     rows = sum(counts)
     x = _rand(rows, d)
     wg, wv = _rand(E, d, f, scale=0.1), _rand(E, d, f, scale=0.1)
