@@ -4,6 +4,7 @@
 #include <torch/extension.h>
 
 #include <cstdlib>
+#include <cstring>
 
 #include "cuda_check.h"
 #include "gemm_tc.cuh"
@@ -51,8 +52,21 @@ CUtensorMap map_b(const at::Tensor& b, bool b_mn, int box_rows) {
   return make_tma_desc(b.data_ptr(), 2, 3, dims, strides, box, true);
 }
 
+// Destination map for the staged stores of the epilogue: 32 x 32 boxes of 16-bit elements, 64-byte swizzle.
+CUtensorMap map_c(const void* base, int64_t cols, int64_t rows, int64_t ld) {
+  const uint64_t dims[2] = {static_cast<uint64_t>(cols), static_cast<uint64_t>(rows)};
+  const uint64_t strides[1] = {static_cast<uint64_t>(ld) * 2};
+  const uint32_t box[2] = {32, 32};
+  return make_tma_desc_sw(base, 2, 2, dims, strides, box, 64);
+}
+
+bool tma_storable(const void* base, int64_t ld) {
+  return reinterpret_cast<uintptr_t>(base) % 16 == 0 && (ld * 2) % 16 == 0;
+}
+
 template <int BN, int EPI>
-void launch(const CUtensorMap& tA, const CUtensorMap (&tB)[3], const Args& args, int tiles, cudaStream_t stream) {
+void launch(const CUtensorMap& tA, const CUtensorMap (&tB)[3], const CUtensorMap (&tC)[3], const Args& args, int tiles,
+            cudaStream_t stream) {
   using S = gemm::Smem<BN>;
   auto kernel = gemm::gemm_tc_kernel<BN, EPI>;
   static bool configured = false;
@@ -62,12 +76,13 @@ void launch(const CUtensorMap& tA, const CUtensorMap (&tB)[3], const Args& args,
   }
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   const int grid = std::max(1, std::min(tiles, sms));
-  kernel<<<grid, gemm::NUM_THREADS, S::TOTAL, stream>>>(tA, tB[0], tB[1], tB[2], args);
+  kernel<<<grid, gemm::NUM_THREADS, S::TOTAL, stream>>>(tA, tB[0], tB[1], tB[2], tC[0], tC[1], tC[2], args);
   NT_KERNEL_CHECK();
 }
 
 template <int EPI>
-void launch_pair(const CUtensorMap& tA, const CUtensorMap (&tB)[3], const Args& args, int tiles, cudaStream_t stream) {
+void launch_pair(const CUtensorMap& tA, const CUtensorMap (&tB)[3], const CUtensorMap (&tC)[3], const Args& args, int tiles,
+                 cudaStream_t stream) {
   auto kernel = gemm::gemm_tc_pair_kernel<EPI>;
   static bool configured = false;
   if (!configured) {
@@ -76,7 +91,7 @@ void launch_pair(const CUtensorMap& tA, const CUtensorMap (&tB)[3], const Args& 
   }
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount & ~1;
   const int grid = std::max(2, std::min(2 * tiles, sms));
-  kernel<<<grid, gemm::NUM_THREADS, gemm::PAIR_SMEM, stream>>>(tA, tB[0], tB[1], tB[2], args);  // clusters of 2 (compile-time attribute)
+  kernel<<<grid, gemm::NUM_THREADS, gemm::PAIR_SMEM, stream>>>(tA, tB[0], tB[1], tB[2], tC[0], tC[1], tC[2], args);  // clusters of 2 (compile-time attribute)
   NT_KERNEL_CHECK();
 }
 
@@ -280,6 +295,30 @@ void gemm_tc(const at::Tensor& A, bool a_mn, const std::vector<at::Tensor>& Bs, 
   }
 
   if (args.M == 0 || args.N == 0) return;
+
+  // ---- staged TMA stores of the epilogue (16-bit outputs of the dense and grouped-M shapes)
+  CUtensorMap tC[3];
+  std::memset(tC, 0, sizeof(tC));
+  static const bool staged_ok = [] { const char* e = std::getenv("NT_GEMM_DIRECT_STORE"); return !(e != nullptr && e[0] == '1'); }();
+  if (staged_ok && mode != gemm::kGroupedK && !args.out_f32 && tma_storable(C0.data_ptr(), args.ldc)) {
+    bool ok = true;
+    if (epilogue == gemm::kEpiStore) {
+      const int64_t cols = ndst > 1 ? args.c_split_size : args.N;
+      for (int i = 0; i < ndst; ++i) ok = ok && tma_storable(Cs[i].data_ptr(), args.ldc);
+      ok = ok && (ndst == 1 || args.c_split_size % 32 == 0);
+      if (ok)
+        for (int i = 0; i < 3; ++i) tC[i] = map_c(Cs[std::min(i, ndst - 1)].data_ptr(), cols, args.M, args.ldc);
+    } else {
+      ok = args.N % 32 == 0;  // a gate chunk must not run into the value half
+      if (ok && epilogue == gemm::kEpiSwigluFwd) ok = tma_storable(args.C2, args.ldc2);
+      if (ok) {
+        tC[0] = map_c(C0.data_ptr(), 2 * args.N, args.M, args.ldc);
+        tC[1] = epilogue == gemm::kEpiSwigluFwd ? map_c(args.C2, args.N, args.M, args.ldc2) : tC[0];
+        tC[2] = tC[0];
+      }
+    }
+    args.c_tma = ok ? 1 : 0;
+  }
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   int m_tiles;
   if (mode == gemm::kDense) m_tiles = (args.M + gemm::BM - 1) / gemm::BM;
@@ -301,9 +340,9 @@ void gemm_tc(const at::Tensor& A, bool a_mn, const std::vector<at::Tensor>& Bs, 
     CUtensorMap ptB[3];
     for (int i = 0; i < 3; ++i) ptB[i] = map_b(Bs[std::min(i, nsrc - 1)], b_mn, gemm::PAIR_BN / 2);
     cudaStream_t pstream = at::cuda::getCurrentCUDAStream();
-    if (epilogue == gemm::kEpiSwigluFwd) launch_pair<gemm::kEpiSwigluFwd>(ptA, ptB, args, ptiles, pstream);
-    else if (epilogue == gemm::kEpiSwigluBwd) launch_pair<gemm::kEpiSwigluBwd>(ptA, ptB, args, ptiles, pstream);
-    else launch_pair<gemm::kEpiStore>(ptA, ptB, args, ptiles, pstream);
+    if (epilogue == gemm::kEpiSwigluFwd) launch_pair<gemm::kEpiSwigluFwd>(ptA, ptB, tC, args, ptiles, pstream);
+    else if (epilogue == gemm::kEpiSwigluBwd) launch_pair<gemm::kEpiSwigluBwd>(ptA, ptB, tC, args, ptiles, pstream);
+    else launch_pair<gemm::kEpiStore>(ptA, ptB, tC, args, ptiles, pstream);
     return;
   }
 
@@ -346,7 +385,7 @@ void gemm_tc(const at::Tensor& A, bool a_mn, const std::vector<at::Tensor>& Bs, 
   for (int i = 0; i < 3; ++i) tB[i] = map_b(Bs[std::min(i, nsrc - 1)], b_mn, box_rows);
 
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
-#define NT_LAUNCH(BN_, EPI_) launch<BN_, EPI_>(tA, tB, args, launch_tiles, stream)
+#define NT_LAUNCH(BN_, EPI_) launch<BN_, EPI_>(tA, tB, tC, args, launch_tiles, stream)
   if (epilogue == gemm::kEpiSwigluFwd) {
     TORCH_CHECK(bn == 256, "SwiGLU forward uses 256-wide tiles");
     NT_LAUNCH(256, gemm::kEpiSwigluFwd);

@@ -29,6 +29,9 @@ constexpr int BK = 64;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int MAX_GROUPS = 256;
 constexpr int NUM_THREADS = 192;
+constexpr int STAGING_SLOT_BYTES = 32 * 64;               // 32 rows x 32 16-bit columns
+constexpr int STAGING_WARP_BYTES = 4 * STAGING_SLOT_BYTES;  // per epilogue warp
+constexpr int STAGING_BYTES = 4 * STAGING_WARP_BYTES;
 
 enum Mode : int { kDense = 0, kGroupedM = 1, kGroupedK = 2 };
 enum BSplit : int { kBNone = 0, kBSplitN = 1, kBSplitK = 2, kBDual = 3 };
@@ -53,6 +56,7 @@ struct Args {
   // tiles go to `ws` ([k_splits][G][M][N]); a second kernel folds them in a fixed order.
   int k_splits;
   float* ws;
+  int c_tma;  // 1: the C tensor maps are valid and full 32-row groups may use staged TMA stores
   StatusWord* status;
 };
 
@@ -75,7 +79,7 @@ struct Smem {
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
   static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8;
   static constexpr int EXTRA_BYTES = 16 + (MAX_GROUPS + 1) * 4;
-  static constexpr int TOTAL = TILE_BYTES + BAR_BYTES + EXTRA_BYTES + 1024;  // + alignment slack
+  static constexpr int TOTAL = TILE_BYTES + STAGING_BYTES + BAR_BYTES + EXTRA_BYTES + 1024;  // + alignment slack
 };
 
 __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
@@ -229,63 +233,153 @@ __device__ __forceinline__ void store_row32(void* base, long long elem_off, int 
   }
 }
 
+// ---- staged stores -------------------------------------------------------------------------
+// A thread of an epilogue warp owns one row of the accumulator, so direct stores make every warp
+// store instruction touch 32 different rows (32 half-used sectors per instruction, and the LSU
+// becomes the bottleneck of short-K problems).  Instead each warp owns four 2 KB slots of shared
+// memory; a 32 row x 32 column chunk is written there (one conflict-free 64-byte row per lane,
+// in the layout of a SWIZZLE_64B tensor map) and one lane hands it to the TMA engine, which
+// writes full 64-byte row segments and clips at the tensor's edges.  The slots form a ring: a
+// slot is rewritten only after the store group that last read it has finished reading.
+struct Stager {
+  uint8_t* slots;             // this warp's four slots
+  const CUtensorMap *map0, *map1, *map2;  // destinations (the host side says which is which per epilogue)
+  int next;                   // ring position
+  int lane;
+  int row0;                   // per tile: global row of the warp's first accumulator lane
+  bool on;                    // per tile: this warp's rows go through the slots (else direct stores)
+};
+
+__device__ __forceinline__ void pack32(const float (&v)[32], int dtype, uint32_t (&w)[16]) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] = pack2(v[2 * i], v[2 * i + 1], dtype);
+}
+
+// This lane's row (32 x 16 bit) into a slot: 16-byte piece j of row r sits at piece j ^ ((r >> 1) & 3).
+__device__ __forceinline__ void stage_row(uint8_t* slot, int lane, const uint32_t (&w)[16]) {
+  const uint32_t base = sm100::smem_u32(slot) + static_cast<uint32_t>(lane) * 64u;
+  const uint32_t sw = (static_cast<uint32_t>(lane) >> 1) & 3u;
+#pragma unroll
+  for (uint32_t j = 0; j < 4; ++j) sm100::st_shared_v4(base + ((j ^ sw) << 4), w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+}
+
+// Before a slot is rewritten: at most PENDING earlier store groups of this warp may still be reading.
+template <int PENDING>
+__device__ __forceinline__ void stager_acquire(const Stager& st) {
+  if (st.lane == 0) sm100::tma_store_wait_read<PENDING>();
+  __syncwarp();
+}
+// After the rows are written: make them visible to the TMA engine.
+__device__ __forceinline__ void stager_publish() {
+  sm100::fence_proxy_async_smem();
+  __syncwarp();
+}
+
 // Drains one accumulator tile (this warp's 32 TMEM lanes = 32 rows) through the epilogue EPI.
 // `t_addr`: TMEM address of the tile's first column in this warp's lanes; `row`: global row of
 // this thread; `row_ok`: the row exists; `have_acc`: the tile had at least one reduction step.
 template <int BN, int EPI>
-__device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, uint32_t t_addr, bool row_ok, bool have_acc, long long row) {
+__device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, uint32_t t_addr, bool row_ok, bool have_acc, long long row,
+                                              Stager& st) {
   using namespace sm100;
   if constexpr (EPI == kEpiStore) {
     const long long grp_off = (args.mode == kGroupedK) ? static_cast<long long>(ti.g) * args.c_group_stride : 0;
     const bool partial = args.mode == kGroupedK && args.k_splits > 1;
     float* ws_tile = partial ? args.ws + (static_cast<long long>(ti.split) * args.G + ti.g) * args.M * args.N : nullptr;
-#pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 32) {
-      const int col = ti.n0 + c0;
-      if (col >= args.N) break;  // uniform across the warp
-      float v[32];
-      if (have_acc) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_addr + c0, r);
-        tmem_ld_wait();
+    // Residual rows are requested one chunk ahead so their latency hides behind the previous chunk.
+    const uint16_t* r_row = reinterpret_cast<const uint16_t*>(args.R) + row * args.ldr;
+    const bool fast_r = args.R != nullptr && row_ok && (reinterpret_cast<uintptr_t>(r_row) & 15u) == 0;
+    uint4 rq[4];
+    auto fetch_r = [&](int col) {
+      if (fast_r && col + 32 <= args.N && col < ti.n0 + BN && (col & 7) == 0) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+        for (int q = 0; q < 4; ++q) rq[q] = __ldg(reinterpret_cast<const uint4*>(r_row + col) + q);
       }
+    };
+    fetch_r(ti.n0);
+    // One 32-column chunk: epilogue math on the raw accumulator words, then the store.
+    auto process = [&](int c0, uint32_t (&r)[32]) {
+      const int col = ti.n0 + c0;
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = have_acc ? __uint_as_float(r[i]) : 0.f;
+      const int valid = min(32, args.N - col);
       if (row_ok && partial) {
-        store_row32(ws_tile, row * args.N + col, min(32, args.N - col), args.dtype, true, v);
-      } else if (row_ok) {
-        const int valid = min(32, args.N - col);
-        if (args.R != nullptr) {
+        store_row32(ws_tile, row * args.N + col, valid, args.dtype, true, v);
+        return;
+      }
+      if (args.R != nullptr) {
+        if (fast_r && valid == 32) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float lo, hi;
+            unpack2(rq[q].x, args.dtype, lo, hi); v[8 * q + 0] += lo; v[8 * q + 1] += hi;
+            unpack2(rq[q].y, args.dtype, lo, hi); v[8 * q + 2] += lo; v[8 * q + 3] += hi;
+            unpack2(rq[q].z, args.dtype, lo, hi); v[8 * q + 4] += lo; v[8 * q + 5] += hi;
+            unpack2(rq[q].w, args.dtype, lo, hi); v[8 * q + 6] += lo; v[8 * q + 7] += hi;
+          }
+        } else if (row_ok) {
           float rr[32];
           load_row32(args.R, row * args.ldr + col, valid, args.dtype, rr);
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] += rr[i];
         }
-        void* dst = args.C[0];
-        int dcol = col;
-        if (args.c_split_size > 0) {
-          const int d = col / args.c_split_size;
-          dst = args.C[d];
-          dcol = col - d * args.c_split_size;
-        }
-        const long long off = grp_off + row * args.ldc + dcol;
-        if (args.accumulate) {
-          if (args.out_f32) {
-            const float* p = reinterpret_cast<const float*>(dst) + off;
+        fetch_r(col + 32);  // the next chunk's residual is in flight during this chunk's stores
+      }
+      void* dst = args.C[0];
+      int dcol = col, d = 0;
+      if (args.c_split_size > 0) {
+        d = col / args.c_split_size;
+        dst = args.C[d];
+        dcol = col - d * args.c_split_size;
+      }
+      const long long off = grp_off + row * args.ldc + dcol;
+      if (row_ok && args.accumulate) {
+        if (args.out_f32) {
+          const float* p = reinterpret_cast<const float*>(dst) + off;
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (i < valid) v[i] += p[i];
-          } else {
-            float old[32];
-            load_row32(dst, off, valid, args.dtype, old);
+          for (int i = 0; i < 32; ++i)
+            if (i < valid) v[i] += p[i];
+        } else {
+          float old[32];
+          load_row32(dst, off, valid, args.dtype, old);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] += old[i];
-          }
+          for (int i = 0; i < 32; ++i) v[i] += old[i];
         }
+      }
+      if (st.on) {
+        uint32_t w[16];
+        pack32(v, args.dtype, w);
+        stager_acquire<3>(st);
+        uint8_t* slot = st.slots + st.next * STAGING_SLOT_BYTES;
+        stage_row(slot, st.lane, w);
+        stager_publish();
+        if (st.lane == 0) {
+          tma_store_2d(d == 0 ? st.map0 : (d == 1 ? st.map1 : st.map2), slot, dcol, st.row0);
+          tma_store_commit();
+        }
+        st.next = (st.next + 1) & 3;
+      } else if (row_ok) {
         store_row32(dst, off, valid, args.dtype, args.out_f32 != 0, v);
+      }
+    };
+    // Chunks that start inside the matrix; the TMEM read of chunk c+1 is in flight during chunk c.
+    const int n_chunks = min(BN / 32, (args.N - ti.n0 + 31) / 32);
+    uint32_t ra[32], rb[32];
+    if (have_acc) tmem_ld_32x32(t_addr, ra);
+#pragma unroll 1
+    for (int c = 0; c < n_chunks; c += 2) {
+      if (have_acc) {
+        tmem_ld_wait_on(ra);
+        if (c + 1 < n_chunks) tmem_ld_32x32(t_addr + (c + 1) * 32, rb);
+      }
+      process(c * 32, ra);
+      if (c + 1 < n_chunks) {
+        if (have_acc) {
+          tmem_ld_wait_on(rb);
+          if (c + 2 < n_chunks) tmem_ld_32x32(t_addr + (c + 2) * 32, ra);
+        }
+        process((c + 1) * 32, rb);
       }
     }
   } else if constexpr (EPI == kEpiSwigluFwd) {
@@ -298,19 +392,35 @@ __device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, 
       tmem_ld_32x32(t_addr + c0, rg);
       tmem_ld_32x32(t_addr + BN / 2 + c0, rv);
       tmem_ld_wait();
-      if (row_ok) {
-        const int valid = min(32, args.N - col);
-        float g[32], u[32], h[32];
+      if (!st.on && !row_ok) continue;
+      const int valid = min(32, args.N - col);
+      float g[32], u[32], h[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          g[i] = __uint_as_float(rg[i]);
-          u[i] = __uint_as_float(rv[i]);
+      for (int i = 0; i < 32; ++i) {
+        g[i] = __uint_as_float(rg[i]);
+        u[i] = __uint_as_float(rv[i]);
+        h[i] = silu_f(g[i]) * u[i];
+      }
+      if (st.on) {
+        // three chunks (gate, value, h) fill three of the four slots: wait for all earlier reads
+        uint32_t w[16];
+        stager_acquire<0>(st);
+        pack32(g, args.dtype, w);
+        stage_row(st.slots, st.lane, w);
+        pack32(u, args.dtype, w);
+        stage_row(st.slots + STAGING_SLOT_BYTES, st.lane, w);
+        pack32(h, args.dtype, w);
+        stage_row(st.slots + 2 * STAGING_SLOT_BYTES, st.lane, w);
+        stager_publish();
+        if (st.lane == 0) {
+          tma_store_2d(st.map0, st.slots, col, st.row0);
+          tma_store_2d(st.map0, st.slots + STAGING_SLOT_BYTES, args.N + col, st.row0);
+          tma_store_2d(st.map1, st.slots + 2 * STAGING_SLOT_BYTES, col, st.row0);
+          tma_store_commit();
         }
-        // round gate / value to the storage dtype first so backward sees what forward used
+      } else {
         store_row32(args.C[0], row * args.ldc + col, valid, args.dtype, false, g);
         store_row32(args.C[0], row * args.ldc + args.N + col, valid, args.dtype, false, u);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) h[i] = silu_f(g[i]) * u[i];
         store_row32(args.C2, row * args.ldc2 + col, valid, args.dtype, false, h);
       }
     }
@@ -350,19 +460,39 @@ __device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, 
       } else if (row_ok) {
         load_row32(args.R, row * args.ldr + col, valid, args.dtype, g);
         load_row32(args.R, row * args.ldr + args.N + col, valid, args.dtype, u);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { g[i] = 0.f; u[i] = 0.f; }
       }
       if (c0 + 32 < BN) fetch(col + 32);  // next chunk's rows are in flight during this chunk's math
       tmem_ld_wait();
-      if (row_ok) {
-        float dg[32], du[32];
+      if (!st.on && !row_ok) continue;
+      float dg[32], du[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float dh = __uint_as_float(r[i]);
-          const float sig = 1.f / (1.f + __expf(-g[i]));
-          const float sl = g[i] * sig;
-          dg[i] = dh * u[i] * (sig * (1.f + g[i] * (1.f - sig)));
-          du[i] = dh * sl;
+      for (int i = 0; i < 32; ++i) {
+        const float dh = __uint_as_float(r[i]);
+        const float sig = 1.f / (1.f + __expf(-g[i]));
+        const float sl = g[i] * sig;
+        dg[i] = dh * u[i] * (sig * (1.f + g[i] * (1.f - sig)));
+        du[i] = dh * sl;
+      }
+      if (st.on) {
+        // two chunks (d gate, d value) per step, alternating between the two halves of the ring
+        uint32_t w[16];
+        stager_acquire<1>(st);
+        uint8_t* slot = st.slots + st.next * STAGING_SLOT_BYTES;
+        pack32(dg, args.dtype, w);
+        stage_row(slot, st.lane, w);
+        pack32(du, args.dtype, w);
+        stage_row(slot + STAGING_SLOT_BYTES, st.lane, w);
+        stager_publish();
+        if (st.lane == 0) {
+          tma_store_2d(st.map0, slot, col, st.row0);
+          tma_store_2d(st.map0, slot + STAGING_SLOT_BYTES, args.N + col, st.row0);
+          tma_store_commit();
         }
+        st.next ^= 2;
+      } else {
         store_row32(args.C[0], row * args.ldc + col, valid, args.dtype, false, dg);
         store_row32(args.C[0], row * args.ldc + args.N + col, valid, args.dtype, false, du);
       }
@@ -374,7 +504,8 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2,
-               const Args args) {
+               const __grid_constant__ CUtensorMap tmC0, const __grid_constant__ CUtensorMap tmC1,
+               const __grid_constant__ CUtensorMap tmC2, const Args args) {
   using namespace sm100;
   using S = Smem<BN>;
   constexpr int STAGES = S::STAGES;
@@ -382,7 +513,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::TILE_BYTES);
+  uint8_t* staging = smem + S::TILE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + STAGING_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tmem_full = empty_bar + STAGES;
   uint64_t* tmem_empty = tmem_full + 2;
@@ -549,6 +681,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    Stager st;
+    st.slots = staging + quarter * STAGING_WARP_BYTES;
+    st.map0 = &tmC0; st.map1 = &tmC1; st.map2 = &tmC2;
+    st.next = 0;
+    st.lane = lane;
     for (int t = blockIdx.x; t < n_total && ok; t += gridDim.x) {
       const Tile ti = get_tile<BN, EPI>(args, tile_start, t);
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, args.status, kKernelGemm, 400 + acc)) { ok = false; break; }
@@ -557,13 +694,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const bool row_ok = row_in_tile < ti.rows_valid;
       const bool have_acc = ti.k_chunks > 0;
       const long long row = static_cast<long long>(ti.m0) + row_in_tile;
+      // Staged stores clip at the matrix edge only: inside a grouped problem they are used for
+      // 32-row groups that lie entirely in the tile's segment.
+      const int warp_rows = max(0, min(32, ti.rows_valid - quarter * 32));
+      st.on = args.c_tma != 0 && warp_rows > 0 && (args.mode == kDense || warp_rows == 32);
+      st.row0 = ti.m0 + quarter * 32;
 
-      epilogue_rows<BN, EPI>(args, ti, t_addr, row_ok, have_acc, row);
+      epilogue_rows<BN, EPI>(args, ti, t_addr, row_ok, have_acc, row, st);
       tc_fence_before();
       mbar_arrive(&tmem_empty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (lane == 0) tma_store_wait_read<0>();  // shared memory stays allocated until the last store has read it
   }
 
   // ---------------------------------------------------------------------- teardown

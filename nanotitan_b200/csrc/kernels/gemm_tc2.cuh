@@ -20,7 +20,7 @@ constexpr int PAIR_BN = 256;   // accumulator columns per tile
 constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_B_BYTES = (PAIR_BN / 2) * BK * 2;  // this CTA's half of B per stage
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_BYTES;
-constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE_BYTES + (2 * PAIR_STAGES + 4) * 8 + 16 + (MAX_GROUPS + 1) * 4 + 1024;
+constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE_BYTES + STAGING_BYTES + (2 * PAIR_STAGES + 4) * 8 + 16 + (MAX_GROUPS + 1) * 4 + 1024;
 
 template <int EPI>
 __device__ __forceinline__ int pair_total_tiles(const Args& a, const int* tile_start) {
@@ -58,7 +58,9 @@ __device__ __forceinline__ Tile pair_get_tile(const Args& a, const int* tile_sta
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
-                    const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2, const Args args) {
+                    const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2,
+                    const __grid_constant__ CUtensorMap tmC0, const __grid_constant__ CUtensorMap tmC1,
+                    const __grid_constant__ CUtensorMap tmC2, const Args args) {
   using namespace sm100;
   constexpr int BN = PAIR_BN;
   constexpr int STAGES = PAIR_STAGES;
@@ -66,7 +68,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * PAIR_STAGE_BYTES);
+  uint8_t* staging = smem + STAGES * PAIR_STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + STAGING_BYTES);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tmem_full = empty_bar + STAGES;
   uint64_t* tmem_empty = tmem_full + 2;
@@ -194,6 +197,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    Stager st;
+    st.slots = staging + quarter * STAGING_WARP_BYTES;
+    st.map0 = &tmC0; st.map1 = &tmC1; st.map2 = &tmC2;
+    st.next = 0;
+    st.lane = lane;
     for (int t = pair_id; t < n_total && ok; t += n_pairs) {
       const Tile ti = pair_get_tile<EPI>(args, tile_start, t, rank);
       if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag, args.status, kKernelGemm, 400 + acc)) { ok = false; break; }
@@ -201,13 +209,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t t_addr = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quarter * 32) << 16);
       const bool row_ok = row_in_tile < ti.rows_valid;
       const long long row = static_cast<long long>(ti.m0) + row_in_tile;
-      epilogue_rows<BN, EPI>(args, ti, t_addr, row_ok, true, row);
+      const int warp_rows = max(0, min(32, ti.rows_valid - quarter * 32));
+      st.on = args.c_tma != 0 && warp_rows > 0 && (args.mode == kDense || warp_rows == 32);
+      st.row0 = ti.m0 + quarter * 32;
+      epilogue_rows<BN, EPI>(args, ti, t_addr, row_ok, true, row, st);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&tmem_empty[acc]), 0));  // the leader's barrier
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (lane == 0) tma_store_wait_read<0>();
   }
 
   // ---------------------------------------------------------------------- teardown
