@@ -73,6 +73,8 @@ def bench_gemm(iters):
     T = 30720
     cases = [("qkv/o proj fwd", T, 512, 512, False, True), ("ffn down fwd", T, 512, 2048, False, True),
              ("ffn up fwd", T, 2048, 512, False, True), ("wgrad 512x2048", 512, 2048, T, True, True),
+             ("wgrad 2048x512", 2048, 512, T, True, True), ("wgrad 512x1536", 512, 1536, T, True, True),
+             ("wgrad unembed", 512, 50257, T, True, True),
              ("dgrad unembed", T, 512, 50257, False, True), ("unembed fwd", T, 50257, 512, False, False),
              ("square 8192", 8192, 8192, 8192, False, False)]
     for name, M, N, K, a_mn, b_mn in cases:
@@ -81,7 +83,10 @@ def bench_gemm(iters):
         b = rnd(K, pad(N), scale=0.05)[:, :N] if b_mn else rnd(N, pad(K), scale=0.05)[:, :K]
         ld = pad(N)
         c = torch.empty(M, ld, device="cuda", dtype=torch.bfloat16)[:, :N]
-        ms = timed(lambda: native.gemm_tc(a, a_mn, [b], b_mn, [c]), iters)
+        if a_mn:  # weight gradient: the training path (reduction cut over the SMs, fp32 partials folded in order)
+            ms = timed(lambda: native.wgrad(a, b, [c]), iters)
+        else:
+            ms = timed(lambda: native.gemm_tc(a, a_mn, [b], b_mn, [c]), iters)
         report(f"gemm_tc {name} M{M} N{N} K{K}", ms, flops=2.0 * M * N * K)
         at, bt = (a.t() if a_mn else a), (b if b_mn else b.t())
         ms = timed(lambda: torch.matmul(at, bt), iters)

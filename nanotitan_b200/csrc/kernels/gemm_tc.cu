@@ -96,7 +96,7 @@ void launch_pair(const CUtensorMap& tA, const CUtensorMap (&tB)[3], const CUtens
 }
 
 bool pair_kernels_enabled() {
-  static const bool v = [] { const char* e = std::getenv("NT_GEMM_PAIR"); return e != nullptr && e[0] == '1'; }();  // opt-in
+  static const bool v = [] { const char* e = std::getenv("NT_GEMM_PAIR"); return !(e != nullptr && e[0] == '0'); }();  // NT_GEMM_PAIR=0 turns it off
   return v;
 }
 
@@ -328,7 +328,9 @@ void gemm_tc(const at::Tensor& A, bool a_mn, const std::vector<at::Tensor>& Bs, 
   // ---- CTA-pair kernel (256 x 256 tiles, cta_group::2) for the non-ragged-reduction shapes
   const bool pair_ok = mode != gemm::kGroupedK && args.N > 128 && args.M >= 256 && ndst == 1 &&
                        (b_split != gemm::kBSplitN || args.b_split_size % gemm::PAIR_BN == 0);
-  const bool use_pair = force_bn == 512 || (force_bn == 0 && pair_ok && pair_kernels_enabled());
+  // Measured on the training shapes: the pair kernel wins from K = 2048 up (it halves the B traffic
+  // per SM), the one-CTA kernel on K = 512 (twice the tiles to balance over the SMs).
+  const bool use_pair = force_bn == 512 || (force_bn == 0 && pair_ok && args.K >= 1024 && pair_kernels_enabled());
   if (use_pair) {
     TORCH_CHECK(pair_ok, "gemm_tc: this problem cannot run on the CTA-pair kernel");
     const int pm = mode == gemm::kDense ? (args.M + gemm::PAIR_BM - 1) / gemm::PAIR_BM
@@ -369,7 +371,8 @@ void gemm_tc(const at::Tensor& A, bool a_mn, const std::vector<at::Tensor>& Bs, 
       (ndst == 1 || args.c_split_size % 4 == 0)) {
     const long long rows_per_group = std::max<long long>(1, a_rows / args.G);
     const long long max_by_depth = std::max<long long>(1, rows_per_group / (8 * gemm::BK));  // >= 8 steps per part
-    long long want = tiles < sms ? (2LL * sms + tiles - 1) / tiles : 1;
+    // two full rounds of work units over the SMs, never a few units into a third round
+    long long want = tiles < sms ? std::max<long long>(1, 2LL * sms / tiles) : 1;
     want = std::min<long long>({want, 32, max_by_depth});
     if (want > 1) {
       args.k_splits = static_cast<int>(want);

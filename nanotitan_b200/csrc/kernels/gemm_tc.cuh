@@ -5,8 +5,9 @@
 // One CTA per SM walks a list of output tiles.  Warp 0 feeds a ring of shared-memory stages
 // with TMA (128-byte swizzle, no multicast); warp 1 issues `tcgen05.mma` (one elected lane)
 // into one of two TMEM accumulators and signals stage release / accumulator-ready through
-// `tcgen05.commit`; warps 2-5 drain the other accumulator with `tcgen05.ld`, apply the
-// epilogue and store, so the epilogue of tile i overlaps the MMAs of tile i+1.
+// `tcgen05.commit`; warps 2-9 drain the other accumulator with `tcgen05.ld`, apply the
+// epilogue and store (through shared memory and TMA), so the epilogue of tile i overlaps the
+// MMAs of tile i+1.
 //
 // Either operand may be K-major (reduction dim contiguous) or MN-major; B may come from up to
 // three tensors (split along N, along K, or as two half-tiles for SwiGLU), C may be split along
@@ -28,10 +29,11 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int MAX_GROUPS = 256;
-constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 8;                      // two per scheduler: one warp's dependent chains hide behind the other's
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;  // TMA warp, MMA warp, epilogue warps
 constexpr int STAGING_SLOT_BYTES = 32 * 64;               // 32 rows x 32 16-bit columns
-constexpr int STAGING_WARP_BYTES = 4 * STAGING_SLOT_BYTES;  // per epilogue warp
-constexpr int STAGING_BYTES = 4 * STAGING_WARP_BYTES;
+constexpr int STAGING_WARP_BYTES = 2 * STAGING_SLOT_BYTES;  // per epilogue warp
+constexpr int STAGING_BYTES = EPI_WARPS * STAGING_WARP_BYTES;
 
 enum Mode : int { kDense = 0, kGroupedM = 1, kGroupedK = 2 };
 enum BSplit : int { kBNone = 0, kBSplitN = 1, kBSplitK = 2, kBDual = 3 };
@@ -236,23 +238,52 @@ __device__ __forceinline__ void store_row32(void* base, long long elem_off, int 
 // ---- staged stores -------------------------------------------------------------------------
 // A thread of an epilogue warp owns one row of the accumulator, so direct stores make every warp
 // store instruction touch 32 different rows (32 half-used sectors per instruction, and the LSU
-// becomes the bottleneck of short-K problems).  Instead each warp owns four 2 KB slots of shared
+// becomes the bottleneck of short-K problems).  Instead each warp owns two 2 KB slots of shared
 // memory; a 32 row x 32 column chunk is written there (one conflict-free 64-byte row per lane,
 // in the layout of a SWIZZLE_64B tensor map) and one lane hands it to the TMA engine, which
-// writes full 64-byte row segments and clips at the tensor's edges.  The slots form a ring: a
-// slot is rewritten only after the store group that last read it has finished reading.
+// writes full 64-byte row segments and clips at the tensor's edges.  A slot is rewritten only
+// after the store group that last read it has finished reading.
 struct Stager {
-  uint8_t* slots;             // this warp's four slots
+  uint8_t* slots;                          // this warp's two slots
   const CUtensorMap *map0, *map1, *map2;  // destinations (the host side says which is which per epilogue)
-  int next;                   // ring position
+  int next;                                // ring position (store epilogue)
   int lane;
-  int row0;                   // per tile: global row of the warp's first accumulator lane
-  bool on;                    // per tile: this warp's rows go through the slots (else direct stores)
+  int row0;                                // per tile: global row of the warp's first accumulator lane
+  bool on;                                 // per tile: this warp's rows go through the slots (else direct stores)
 };
 
+// 32 floats -> 16 words of the storage dtype; the dtype test is one uniform branch per chunk.
 __device__ __forceinline__ void pack32(const float (&v)[32], int dtype, uint32_t (&w)[16]) {
+  if (dtype == 1) {
 #pragma unroll
-  for (int i = 0; i < 16; ++i) w[i] = pack2(v[2 * i], v[2 * i + 1], dtype);
+    for (int i = 0; i < 16; ++i) {
+      __nv_bfloat162 t = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&t);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      __half2 t = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&t);
+    }
+  }
+}
+// 32 stored values (four 16-byte pieces) -> floats.
+__device__ __forceinline__ void unpack32(const uint4 (&q)[4], int dtype, float (&out)[32]) {
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(q);
+  if (dtype == 1) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+      out[2 * i] = f.x; out[2 * i + 1] = f.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      out[2 * i] = f.x; out[2 * i + 1] = f.y;
+    }
+  }
 }
 
 // This lane's row (32 x 16 bit) into a slot: 16-byte piece j of row r sits at piece j ^ ((r >> 1) & 3).
@@ -275,12 +306,14 @@ __device__ __forceinline__ void stager_publish() {
   __syncwarp();
 }
 
-// Drains one accumulator tile (this warp's 32 TMEM lanes = 32 rows) through the epilogue EPI.
+// Drains this warp's share of one accumulator tile through the epilogue EPI: its 32 TMEM lanes
+// (= 32 rows) of accumulator columns [c_lo, c_hi) (multiples of 32; for the SwiGLU forward the
+// range counts output columns, each of which has a gate and a value accumulator column).
 // `t_addr`: TMEM address of the tile's first column in this warp's lanes; `row`: global row of
 // this thread; `row_ok`: the row exists; `have_acc`: the tile had at least one reduction step.
 template <int BN, int EPI>
 __device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, uint32_t t_addr, bool row_ok, bool have_acc, long long row,
-                                              Stager& st) {
+                                              int c_lo, int c_hi, Stager& st) {
   using namespace sm100;
   if constexpr (EPI == kEpiStore) {
     const long long grp_off = (args.mode == kGroupedK) ? static_cast<long long>(ti.g) * args.c_group_stride : 0;
@@ -291,18 +324,22 @@ __device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, 
     const bool fast_r = args.R != nullptr && row_ok && (reinterpret_cast<uintptr_t>(r_row) & 15u) == 0;
     uint4 rq[4];
     auto fetch_r = [&](int col) {
-      if (fast_r && col + 32 <= args.N && col < ti.n0 + BN && (col & 7) == 0) {
+      if (fast_r && col + 32 <= args.N && col < ti.n0 + c_hi) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) rq[q] = __ldg(reinterpret_cast<const uint4*>(r_row + col) + q);
       }
     };
-    fetch_r(ti.n0);
+    fetch_r(ti.n0 + c_lo);
     // One 32-column chunk: epilogue math on the raw accumulator words, then the store.
     auto process = [&](int c0, uint32_t (&r)[32]) {
       const int col = ti.n0 + c0;
+      if (!have_acc) {  // uniform; only the ragged reductions have empty tiles
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = 0u;
+      }
       float v[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = have_acc ? __uint_as_float(r[i]) : 0.f;
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
       const int valid = min(32, args.N - col);
       if (row_ok && partial) {
         store_row32(ws_tile, row * args.N + col, valid, args.dtype, true, v);
@@ -310,14 +347,10 @@ __device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, 
       }
       if (args.R != nullptr) {
         if (fast_r && valid == 32) {
+          float rr[32];
+          unpack32(rq, args.dtype, rr);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            float lo, hi;
-            unpack2(rq[q].x, args.dtype, lo, hi); v[8 * q + 0] += lo; v[8 * q + 1] += hi;
-            unpack2(rq[q].y, args.dtype, lo, hi); v[8 * q + 2] += lo; v[8 * q + 3] += hi;
-            unpack2(rq[q].z, args.dtype, lo, hi); v[8 * q + 4] += lo; v[8 * q + 5] += hi;
-            unpack2(rq[q].w, args.dtype, lo, hi); v[8 * q + 6] += lo; v[8 * q + 7] += hi;
-          }
+          for (int i = 0; i < 32; ++i) v[i] += rr[i];
         } else if (row_ok) {
           float rr[32];
           load_row32(args.R, row * args.ldr + col, valid, args.dtype, rr);
@@ -350,7 +383,7 @@ __device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, 
       if (st.on) {
         uint32_t w[16];
         pack32(v, args.dtype, w);
-        stager_acquire<3>(st);
+        stager_acquire<1>(st);
         uint8_t* slot = st.slots + st.next * STAGING_SLOT_BYTES;
         stage_row(slot, st.lane, w);
         stager_publish();
@@ -358,26 +391,27 @@ __device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, 
           tma_store_2d(d == 0 ? st.map0 : (d == 1 ? st.map1 : st.map2), slot, dcol, st.row0);
           tma_store_commit();
         }
-        st.next = (st.next + 1) & 3;
+        st.next ^= 1;
       } else if (row_ok) {
         store_row32(dst, off, valid, args.dtype, args.out_f32 != 0, v);
       }
     };
     // Chunks that start inside the matrix; the TMEM read of chunk c+1 is in flight during chunk c.
-    const int n_chunks = min(BN / 32, (args.N - ti.n0 + 31) / 32);
+    const int c_begin = c_lo / 32;
+    const int c_end = min(c_hi / 32, (args.N - ti.n0 + 31) / 32);
     uint32_t ra[32], rb[32];
-    if (have_acc) tmem_ld_32x32(t_addr, ra);
+    if (have_acc && c_begin < c_end) tmem_ld_32x32(t_addr + c_begin * 32, ra);
 #pragma unroll 1
-    for (int c = 0; c < n_chunks; c += 2) {
+    for (int c = c_begin; c < c_end; c += 2) {
       if (have_acc) {
         tmem_ld_wait_on(ra);
-        if (c + 1 < n_chunks) tmem_ld_32x32(t_addr + (c + 1) * 32, rb);
+        if (c + 1 < c_end) tmem_ld_32x32(t_addr + (c + 1) * 32, rb);
       }
       process(c * 32, ra);
-      if (c + 1 < n_chunks) {
+      if (c + 1 < c_end) {
         if (have_acc) {
           tmem_ld_wait_on(rb);
-          if (c + 2 < n_chunks) tmem_ld_32x32(t_addr + (c + 2) * 32, ra);
+          if (c + 2 < c_end) tmem_ld_32x32(t_addr + (c + 2) * 32, ra);
         }
         process((c + 1) * 32, rb);
       }
@@ -385,7 +419,7 @@ __device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, 
   } else if constexpr (EPI == kEpiSwigluFwd) {
     // accumulator columns [0, BN/2) = gate, [BN/2, BN) = value, for output columns n0 .. n0+BN/2
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+    for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
       const int col = ti.n0 + c0;
       if (col >= args.N) break;
       uint32_t rg[32], rv[32];
@@ -394,31 +428,42 @@ __device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, 
       tmem_ld_wait();
       if (!st.on && !row_ok) continue;
       const int valid = min(32, args.N - col);
-      float g[32], u[32], h[32];
+      float g[32], u[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         g[i] = __uint_as_float(rg[i]);
         u[i] = __uint_as_float(rv[i]);
-        h[i] = silu_f(g[i]) * u[i];
       }
       if (st.on) {
-        // three chunks (gate, value, h) fill three of the four slots: wait for all earlier reads
+        // gate and value chunks fill the two slots and leave; h is computed while the TMA engine
+        // reads them and then reuses the first slot
         uint32_t w[16];
         stager_acquire<0>(st);
         pack32(g, args.dtype, w);
         stage_row(st.slots, st.lane, w);
         pack32(u, args.dtype, w);
         stage_row(st.slots + STAGING_SLOT_BYTES, st.lane, w);
-        pack32(h, args.dtype, w);
-        stage_row(st.slots + 2 * STAGING_SLOT_BYTES, st.lane, w);
         stager_publish();
         if (st.lane == 0) {
           tma_store_2d(st.map0, st.slots, col, st.row0);
+          tma_store_commit();
           tma_store_2d(st.map0, st.slots + STAGING_SLOT_BYTES, args.N + col, st.row0);
-          tma_store_2d(st.map1, st.slots + 2 * STAGING_SLOT_BYTES, col, st.row0);
+          tma_store_commit();
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) g[i] = silu_f(g[i]) * u[i];
+        pack32(g, args.dtype, w);
+        stager_acquire<1>(st);  // the gate store has read the first slot
+        stage_row(st.slots, st.lane, w);
+        stager_publish();
+        if (st.lane == 0) {
+          tma_store_2d(st.map1, st.slots, col, st.row0);
           tma_store_commit();
         }
       } else {
+        float h[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) h[i] = silu_f(g[i]) * u[i];
         store_row32(args.C[0], row * args.ldc + col, valid, args.dtype, false, g);
         store_row32(args.C[0], row * args.ldc + args.N + col, valid, args.dtype, false, u);
         store_row32(args.C2, row * args.ldc2 + col, valid, args.dtype, false, h);
@@ -440,9 +485,9 @@ __device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, 
         }
       }
     };
-    fetch(ti.n0);
+    fetch(ti.n0 + c_lo);
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 32) {
+    for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
       const int col = ti.n0 + c0;
       if (col >= args.N) break;
       uint32_t r[32];
@@ -450,13 +495,8 @@ __device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, 
       float g[32], u[32];
       const int valid = min(32, args.N - col);
       if (fast && valid == 32) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          unpack2(gq[v].x, args.dtype, g[8 * v + 0], g[8 * v + 1]); unpack2(gq[v].y, args.dtype, g[8 * v + 2], g[8 * v + 3]);
-          unpack2(gq[v].z, args.dtype, g[8 * v + 4], g[8 * v + 5]); unpack2(gq[v].w, args.dtype, g[8 * v + 6], g[8 * v + 7]);
-          unpack2(uq[v].x, args.dtype, u[8 * v + 0], u[8 * v + 1]); unpack2(uq[v].y, args.dtype, u[8 * v + 2], u[8 * v + 3]);
-          unpack2(uq[v].z, args.dtype, u[8 * v + 4], u[8 * v + 5]); unpack2(uq[v].w, args.dtype, u[8 * v + 6], u[8 * v + 7]);
-        }
+        unpack32(gq, args.dtype, g);
+        unpack32(uq, args.dtype, u);
       } else if (row_ok) {
         load_row32(args.R, row * args.ldr + col, valid, args.dtype, g);
         load_row32(args.R, row * args.ldr + args.N + col, valid, args.dtype, u);
@@ -464,7 +504,7 @@ __device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, 
 #pragma unroll
         for (int i = 0; i < 32; ++i) { g[i] = 0.f; u[i] = 0.f; }
       }
-      if (c0 + 32 < BN) fetch(col + 32);  // next chunk's rows are in flight during this chunk's math
+      if (c0 + 32 < c_hi) fetch(col + 32);  // next chunk's rows are in flight during this chunk's math
       tmem_ld_wait();
       if (!st.on && !row_ok) continue;
       float dg[32], du[32];
@@ -477,21 +517,18 @@ __device__ __forceinline__ void epilogue_rows(const Args& args, const Tile& ti, 
         du[i] = dh * sl;
       }
       if (st.on) {
-        // two chunks (d gate, d value) per step, alternating between the two halves of the ring
         uint32_t w[16];
-        stager_acquire<1>(st);
-        uint8_t* slot = st.slots + st.next * STAGING_SLOT_BYTES;
+        stager_acquire<0>(st);
         pack32(dg, args.dtype, w);
-        stage_row(slot, st.lane, w);
+        stage_row(st.slots, st.lane, w);
         pack32(du, args.dtype, w);
-        stage_row(slot + STAGING_SLOT_BYTES, st.lane, w);
+        stage_row(st.slots + STAGING_SLOT_BYTES, st.lane, w);
         stager_publish();
         if (st.lane == 0) {
-          tma_store_2d(st.map0, slot, col, st.row0);
-          tma_store_2d(st.map0, slot + STAGING_SLOT_BYTES, args.N + col, st.row0);
+          tma_store_2d(st.map0, st.slots, col, st.row0);
+          tma_store_2d(st.map0, st.slots + STAGING_SLOT_BYTES, args.N + col, st.row0);
           tma_store_commit();
         }
-        st.next ^= 2;
       } else {
         store_row32(args.C[0], row * args.ldc + col, valid, args.dtype, false, dg);
         store_row32(args.C[0], row * args.ldc + args.N + col, valid, args.dtype, false, du);
@@ -532,7 +569,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tmem_full[i], 1);
-      mbar_init(&tmem_empty[i], 128);
+      mbar_init(&tmem_empty[i], EPI_WARPS);
     }
     *abort_flag = 0u;
     fence_barrier_init();
@@ -675,14 +712,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (acc == 0) acc_phase ^= 1u;
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // A warp reads the TMEM lanes of its quarter (warp index mod 4); warps 2-5 drain the first
+    // half of the tile's columns, warps 6-9 the second half.
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int SPAN = (EPI == kEpiSwigluFwd ? BN / 2 : BN) / 2;  // columns per warp
+    const int c_lo = half * SPAN, c_hi = c_lo + SPAN;
     const int row_in_tile = quarter * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     Stager st;
-    st.slots = staging + quarter * STAGING_WARP_BYTES;
+    st.slots = staging + (warp - 2) * STAGING_WARP_BYTES;
     st.map0 = &tmC0; st.map1 = &tmC1; st.map2 = &tmC2;
     st.next = 0;
     st.lane = lane;
@@ -700,9 +742,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       st.on = args.c_tma != 0 && warp_rows > 0 && (args.mode == kDense || warp_rows == 32);
       st.row0 = ti.m0 + quarter * 32;
 
-      epilogue_rows<BN, EPI>(args, ti, t_addr, row_ok, have_acc, row, st);
+      epilogue_rows<BN, EPI>(args, ti, t_addr, row_ok, have_acc, row, c_lo, c_hi, st);
       tc_fence_before();
-      mbar_arrive(&tmem_empty[acc]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }

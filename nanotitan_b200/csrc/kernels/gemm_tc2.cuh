@@ -83,7 +83,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&tmem_full[i], 1); mbar_init(&tmem_empty[i], 8); }  // 4 warps x 2 CTAs
+    for (int i = 0; i < 2; ++i) { mbar_init(&tmem_full[i], 1); mbar_init(&tmem_empty[i], 2 * EPI_WARPS); }  // both CTAs' epilogue warps
     *abort_flag = 0u;
     fence_barrier_init();
     prefetch_tmap(&tmA);
@@ -191,14 +191,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+    // ------------------------------------------------------------------ epilogue (warps 2..9 of both CTAs)
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int SPAN = (EPI == kEpiSwigluFwd ? BN / 2 : BN) / 2;
+    const int c_lo = half * SPAN, c_hi = c_lo + SPAN;
     const int row_in_tile = quarter * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     Stager st;
-    st.slots = staging + quarter * STAGING_WARP_BYTES;
+    st.slots = staging + (warp - 2) * STAGING_WARP_BYTES;
     st.map0 = &tmC0; st.map1 = &tmC1; st.map2 = &tmC2;
     st.next = 0;
     st.lane = lane;
@@ -212,7 +215,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int warp_rows = max(0, min(32, ti.rows_valid - quarter * 32));
       st.on = args.c_tma != 0 && warp_rows > 0 && (args.mode == kDense || warp_rows == 32);
       st.row0 = ti.m0 + quarter * 32;
-      epilogue_rows<BN, EPI>(args, ti, t_addr, row_ok, true, row, st);
+      epilogue_rows<BN, EPI>(args, ti, t_addr, row_ok, true, row, c_lo, c_hi, st);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&tmem_empty[acc]), 0));  // the leader's barrier
