@@ -58,7 +58,8 @@ def main():
     agg = collections.defaultdict(lambda: [0, 0.0])
     for ev in prof.events():
         if ev.device_type == torch.autograd.DeviceType.CUDA:
-            name = re.sub(r"\(.*", "", ev.name)
+            name = ev.name.replace("(anonymous namespace)::", "")
+            name = re.sub(r"\(.*", "", name)
             name = re.sub(r"^void ", "", name)
             dur = getattr(ev, "device_time_total", None) or getattr(ev, "cuda_time_total", 0.0)
             agg[name[:90]][0] += 1

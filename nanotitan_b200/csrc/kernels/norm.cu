@@ -62,7 +62,7 @@ template <typename T, int VEC>
 __global__ void __launch_bounds__(LN_WARPS * 32)
 ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
               const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx,
-              float* __restrict__ part_gamma, float* __restrict__ part_beta, long long rows, int d) {
+              const T* __restrict__ dres, float* __restrict__ part_gamma, float* __restrict__ part_beta, long long rows, int d) {
   extern __shared__ float acc[];  // [2][LN_WARPS][d]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* ag = acc + warp * d;
@@ -102,6 +102,11 @@ ln_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __rest
         const float xhat = (xv[i] - mean) * rstd;
         xv[i] = rstd * (gv[i] * dv[i] - s1 - xhat * s2);
       }
+      if (dres != nullptr) {  // gradient that reached x on the path around the normalisation
+        load_vec<T, VEC>(dres + row * d + c, dv);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) xv[i] += dv[i];
+      }
       store_vec<T, VEC>(dx + row * d + c, xv);
     }
   }
@@ -125,7 +130,7 @@ template <typename T, int VEC, int CHUNKS>
 __global__ void __launch_bounds__(LN_WARPS * 32)
 ln_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma,
                   const float* __restrict__ mean_in, const float* __restrict__ rstd_in, T* __restrict__ dx,
-                  float* __restrict__ part_gamma, float* __restrict__ part_beta, long long rows, int d) {
+                  const T* __restrict__ dres, float* __restrict__ part_gamma, float* __restrict__ part_beta, long long rows, int d) {
   extern __shared__ float acc[];  // [2][LN_WARPS][d], used once at the end
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float gv[CHUNKS][VEC], ag[CHUNKS][VEC], ab[CHUNKS][VEC];
@@ -167,6 +172,12 @@ ln_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __
         float out[VEC];
 #pragma unroll
         for (int i = 0; i < VEC; ++i) out[i] = rstd * (gv[j][i] * dv[j][i] - s1 - xh[j][i] * s2);
+        if (dres != nullptr) {  // gradient that reached x on the path around the normalisation
+          float extra[VEC];
+          load_vec<T, VEC>(dres + row * d + c, extra);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) out[i] += extra[i];
+        }
         store_vec<T, VEC>(dx + row * d + c, out);
       }
     }
@@ -243,9 +254,12 @@ std::vector<at::Tensor> layer_norm_fwd(const at::Tensor& x, const at::Tensor& ga
 }
 
 std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
-                                       const at::Tensor& mean, const at::Tensor& rstd) {
+                                       const at::Tensor& mean, const at::Tensor& rstd, const c10::optional<at::Tensor>& dres) {
   TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && x.is_contiguous() && gamma.is_contiguous(), "layer_norm_bwd: contiguous CUDA tensors");
   TORCH_CHECK(dy.scalar_type() == x.scalar_type(), "dy and x must share a dtype");
+  if (dres.has_value())
+    TORCH_CHECK(dres->is_cuda() && dres->is_contiguous() && dres->scalar_type() == x.scalar_type() && dres->numel() == x.numel(),
+                "layer_norm_bwd: the extra gradient must match x");
   c10::cuda::CUDAGuard guard(x.device());
   const int d = static_cast<int>(x.size(-1));
   const long long rows = x.numel() / d;
@@ -262,11 +276,13 @@ std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x
   auto part_b = at::empty({grid, d}, x.options().dtype(at::kFloat));
   NT_DISPATCH_FLOAT(x.scalar_type(), "layer_norm_bwd", [&] {
     constexpr int V = 16 / sizeof(scalar_t);
-    const bool vec = d % V == 0 && is_aligned16(x.data_ptr()) && is_aligned16(dy.data_ptr()) && is_aligned16(gamma.data_ptr());
+    const scalar_t* extra = dres.has_value() ? dres->data_ptr<scalar_t>() : nullptr;
+    const bool vec = d % V == 0 && is_aligned16(x.data_ptr()) && is_aligned16(dy.data_ptr()) && is_aligned16(gamma.data_ptr()) &&
+                     is_aligned16(extra);
     auto launch = [&](auto kernel) {
       if (smem > 48 * 1024) NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
       kernel<<<grid, LN_WARPS * 32, smem, stream>>>(dy.data_ptr<scalar_t>(), x.data_ptr<scalar_t>(), gamma.data_ptr<scalar_t>(),
-          mean.data_ptr<float>(), rstd.data_ptr<float>(), dx.data_ptr<scalar_t>(), part_g.data_ptr<float>(), part_b.data_ptr<float>(), rows, d);
+          mean.data_ptr<float>(), rstd.data_ptr<float>(), dx.data_ptr<scalar_t>(), extra, part_g.data_ptr<float>(), part_b.data_ptr<float>(), rows, d);
     };
     if (vec && d <= 32 * V) launch(ln_bwd_reg_kernel<scalar_t, V, 1>);
     else if (vec && d <= 64 * V) launch(ln_bwd_reg_kernel<scalar_t, V, 2>);

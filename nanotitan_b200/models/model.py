@@ -109,6 +109,10 @@ class LayerNorm(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.layer_norm(x, self.gamma, self.beta, self.EPS)
 
+    def forward_residual(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """(norm(x), x) with x routed through the norm's autograd node (see `ops.layer_norm_residual`)."""
+        return ops.layer_norm_residual(x, self.gamma, self.beta, self.EPS)
+
 
 class MultiHeadAttention(nn.Module):
     def __init__(self, cfg):
@@ -154,8 +158,10 @@ class TransformerLayer(nn.Module):
         )
 
     def forward(self, x: torch.Tensor) -> tuple[torch.Tensor, MoELayerStats]:
-        x = self.attn(self.attn_norm(x), residual=x)
-        x, layer_stats = self.ffn(self.ffn_norm(x), residual=x)
+        h, x = self.attn_norm.forward_residual(x)
+        x = self.attn(h, residual=x)
+        h, x = self.ffn_norm.forward_residual(x)
+        x, layer_stats = self.ffn(h, residual=x)
         return x, layer_stats
 
 

@@ -39,6 +39,16 @@ def layer_norm(x, gamma, beta, eps: float = 1e-8):
     return ref.layer_norm(x, gamma, beta, eps)
 
 
+def layer_norm_residual(x, gamma, beta, eps: float = 1e-8):
+    """(LayerNorm(x), x) for `x + f(LayerNorm(x))`: pass the second value on as the residual and
+    the two gradients of x are summed inside the LayerNorm-backward kernel."""
+    if use_native("layer_norm", x, any_dtype=True):
+        from nanotitan_b200.ops import native
+
+        return native.layer_norm_residual(x, gamma, beta, eps)
+    return ref.layer_norm(x, gamma, beta, eps), x
+
+
 def linear(x, w, residual=None):
     """y = x @ w (+ residual); w is [in, out]."""
     if use_native("linear", x):
@@ -89,6 +99,7 @@ __all__ = [
     "ref",
     "use_native",
     "layer_norm",
+    "layer_norm_residual",
     "linear",
     "causal_attention",
     "qkv_attention",

@@ -170,6 +170,35 @@ def layer_norm(x, gamma, beta, eps=1e-8):
     return _LayerNorm.apply(x, gamma, beta, eps)
 
 
+class _LayerNormResidual(torch.autograd.Function):
+    """(LayerNorm(x), x) for a pre-norm residual block `x + f(LayerNorm(x))`: the second output is x
+    itself, routed through this node so that backward receives the residual path's gradient next
+    to the normalised path's and writes their sum in the LayerNorm-backward kernel (autograd would
+    otherwise add the two with a separate element-wise pass)."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps):
+        xc = x.contiguous()
+        y, mean, rstd = get_ext().layer_norm_fwd(xc, gamma.contiguous(), beta.contiguous(), eps)
+        ctx.save_for_backward(xc, gamma, mean, rstd)
+        return y, xc.view_as(xc)
+
+    @staticmethod
+    def backward(ctx, dy, dpass):
+        x, gamma, mean, rstd = ctx.saved_tensors
+        if dy is None:
+            return dpass, None, None, None
+        dres = None if dpass is None else dpass.contiguous()
+        dx, dgamma, dbeta = get_ext().layer_norm_bwd(dy.contiguous(), x, gamma.contiguous(), mean, rstd, dres)
+        return dx, dgamma.to(gamma.dtype), dbeta.to(gamma.dtype), None
+
+
+def layer_norm_residual(x, gamma, beta, eps=1e-8):
+    if gamma.dtype != x.dtype:
+        gamma, beta = gamma.to(x.dtype), beta.to(x.dtype)
+    return _LayerNormResidual.apply(x, gamma, beta, eps)
+
+
 # ------------------------------------------------------------------------------- attention
 def causal_attention(q, k, v, scale=None):
     """[B, S, H, Dh] causal attention on the tcgen05 flash kernels."""

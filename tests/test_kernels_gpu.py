@@ -43,6 +43,34 @@ def test_layer_norm_forward_backward(dtype, rows, d):
     _close(b.grad, bf.grad, dtype, 4 * rows**0.5)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,d", [(33, 512), (257, 100), (16, 2048)])
+def test_layer_norm_residual_sums_both_gradients(dtype, rows, d):
+    """(norm(x), x): the gradient of the pass-through output is added to dx inside the backward kernel."""
+    from nanotitan_b200.ops import native
+
+    torch.manual_seed(3)
+    x = (torch.randn(rows, d, device="cuda") * 2 + 0.5).to(dtype).requires_grad_()
+    g = (torch.rand(d, device="cuda") + 0.5).to(dtype).requires_grad_()
+    b = torch.randn(d, device="cuda").to(dtype).requires_grad_()
+    y, xp = native.layer_norm_residual(x, g, b, 1e-8)
+    assert xp.data_ptr() == x.data_ptr()
+    dy = torch.randn(rows, d, device="cuda").to(dtype)
+    dp = torch.randn(rows, d, device="cuda").to(dtype)
+    torch.autograd.backward([y, xp], [dy, dp])
+    xf, gf, bf = (t.detach().float().requires_grad_() for t in (x, g, b))
+    yf = ref.layer_norm(xf, gf, bf, 1e-8)
+    torch.autograd.backward([yf, xf * 1.0], [dy.float(), dp.float()])
+    _close(y, yf, dtype, 4)
+    _close(x.grad, xf.grad, dtype, 8)
+    _close(g.grad, gf.grad, dtype, 4 * rows**0.5)
+    # only one of the two outputs used downstream
+    x2 = x.detach().clone().requires_grad_()
+    y2, xp2 = native.layer_norm_residual(x2, g.detach(), b.detach(), 1e-8)
+    xp2.backward(dp)
+    torch.testing.assert_close(x2.grad, dp)
+
+
 # ------------------------------------------------------------------ cross entropy
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows,vocab", [(5, 11), (64, 1000), (16, 50257)])
