@@ -57,6 +57,57 @@ ln_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __r
   }
 }
 
+// Register-resident forward for d <= CHUNKS * 32 * VEC: the row is read from memory once (all of a
+// lane's 16-byte pieces requested before the first is used) and the two reductions run on registers.
+template <typename T, int VEC, int CHUNKS>
+__global__ void __launch_bounds__(LN_WARPS * 32)
+ln_fwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
+                  float* __restrict__ mean_out, float* __restrict__ rstd_out, long long rows, int d, float eps) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * LN_WARPS + warp;
+  if (row >= rows) return;
+  float v[CHUNKS][VEC];
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) {
+    const int c = (j * 32 + lane) * VEC;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[j][i] = 0.f;
+    if (c < d) load_vec<T, VEC>(x + row * d + c, v[j]);
+  }
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j)
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) sum += v[j][i];
+  const float mean = warp_sum(sum) / d;
+  float sq = 0.f;
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) {
+    const int c = (j * 32 + lane) * VEC;
+    if (c < d) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) sq += (v[j][i] - mean) * (v[j][i] - mean);
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(sq) / d + eps);
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) {
+    const int c = (j * 32 + lane) * VEC;
+    if (c < d) {
+      float g[VEC], b[VEC];
+      load_vec<T, VEC>(gamma + c, g);
+      load_vec<T, VEC>(beta + c, b);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[j][i] = (v[j][i] - mean) * rstd * g[i] + b[i];
+      store_vec<T, VEC>(y + row * d + c, v[j]);
+    }
+  }
+  if (lane == 0) {
+    mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
+}
+
 // dx = rstd * (gy - mean(gy) - xhat * mean(gy * xhat)), gy = gamma * dy.
 template <typename T, int VEC>
 __global__ void __launch_bounds__(LN_WARPS * 32)
@@ -141,8 +192,22 @@ ln_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __
     for (int i = 0; i < VEC; ++i) { ag[j][i] = 0.f; ab[j][i] = 0.f; gv[j][i] = 0.f; }
     if (c < d) load_vec<T, VEC>(gamma + c, gv[j]);
   }
-  for (long long row = static_cast<long long>(blockIdx.x) * LN_WARPS + warp; row < rows;
-       row += static_cast<long long>(gridDim.x) * LN_WARPS) {
+  // While a row is reduced, the warp's next row is pulled into L2 (one request per 128-byte line,
+  // no registers held), so its loads in the next iteration do not wait for DRAM.
+  const long long stride = static_cast<long long>(gridDim.x) * LN_WARPS;
+  for (long long row = static_cast<long long>(blockIdx.x) * LN_WARPS + warp; row < rows; row += stride) {
+    if (row + stride < rows && (lane & 7) == 0) {
+#pragma unroll
+      for (int j = 0; j < CHUNKS; ++j) {
+        const int c = (j * 32 + lane) * VEC;
+        if (c < d) {
+          const long long o = (row + stride) * d + c;
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(x + o));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(dy + o));
+          if (dres != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(dres + o));
+        }
+      }
+    }
     const float mean = mean_in[row], rstd = rstd_in[row];
     float xh[CHUNKS][VEC], dv[CHUNKS][VEC];
     float s1 = 0.f, s2 = 0.f;
@@ -242,7 +307,14 @@ std::vector<at::Tensor> layer_norm_fwd(const at::Tensor& x, const at::Tensor& ga
   NT_DISPATCH_FLOAT(x.scalar_type(), "layer_norm_fwd", [&] {
     constexpr int V = 16 / sizeof(scalar_t);
     const bool vec = d % V == 0 && is_aligned16(x.data_ptr()) && is_aligned16(gamma.data_ptr()) && is_aligned16(beta.data_ptr());
-    if (vec)
+    auto launch = [&](auto kernel) {
+      kernel<<<grid, LN_WARPS * 32, 0, stream>>>(x.data_ptr<scalar_t>(), gamma.data_ptr<scalar_t>(), beta.data_ptr<scalar_t>(),
+          y.data_ptr<scalar_t>(), mean.data_ptr<float>(), rstd.data_ptr<float>(), rows, d, static_cast<float>(eps));
+    };
+    if (vec && d <= 32 * V) launch(ln_fwd_reg_kernel<scalar_t, V, 1>);
+    else if (vec && d <= 64 * V) launch(ln_fwd_reg_kernel<scalar_t, V, 2>);
+    else if (vec && d <= 128 * V) launch(ln_fwd_reg_kernel<scalar_t, V, 4>);
+    else if (vec)
       ln_fwd_kernel<scalar_t, V><<<grid, LN_WARPS * 32, 0, stream>>>(x.data_ptr<scalar_t>(), gamma.data_ptr<scalar_t>(), beta.data_ptr<scalar_t>(),
           y.data_ptr<scalar_t>(), mean.data_ptr<float>(), rstd.data_ptr<float>(), rows, d, static_cast<float>(eps));
     else

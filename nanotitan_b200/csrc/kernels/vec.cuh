@@ -54,6 +54,14 @@ __device__ __forceinline__ void load_vec(const T* p, float (&out)[VEC]) {
     for (int i = 0; i < VEC; ++i) out[i] = elem_to_float<T>(p[i]);
   }
 }
+// A 16-byte piece kept in its stored form (four registers) until it is needed as floats.
+template <typename T, int VEC>
+__device__ __forceinline__ void unpack_vec(const uint4& raw, float (&out)[VEC]) {
+  static_assert(VEC * sizeof(T) == 16, "unpack_vec is for 16-byte pieces");
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) out[i] = elem_to_float<T>(e[i]);
+}
 template <typename T, int VEC>
 __device__ __forceinline__ void store_vec(T* p, const float (&v)[VEC]) {
   if constexpr (VEC * sizeof(T) == 16) {
