@@ -39,7 +39,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ep_push_rows", &nt::ep_push_rows, "Push rows into peers' staging buffers (expert-parallel dispatch / return)");
   m.def("layer_norm_fwd", &nt::layer_norm_fwd);
   m.def("layer_norm_bwd", &nt::layer_norm_bwd, py::arg("dy"), py::arg("x"), py::arg("gamma"), py::arg("mean"), py::arg("rstd"),
-        py::arg("dres") = py::none());
+        py::arg("dres") = py::none(), py::arg("dgamma_out") = py::none(), py::arg("dbeta_out") = py::none());
   m.def("cross_entropy_fwd_bwd", &nt::cross_entropy_fwd_bwd);
   m.def("adamw_step", &nt::adamw_step);
   m.def("router_topk", &nt::router_topk);

@@ -274,7 +274,12 @@ ln_bwd_reg_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __
 // out[c] = sum over `parts` rows of in[p][c].  Block = 32 columns x 8 row groups; each group adds
 // its rows in index order and the 8 group sums are added in group order, so the result does not
 // depend on scheduling.
-__global__ void column_sum_kernel(const float* __restrict__ in, float* __restrict__ out, int parts, int d) {
+template <typename TOut>
+__global__ void column_sum_kernel(const float* __restrict__ in0, const float* __restrict__ in1, TOut* __restrict__ out0,
+                                  TOut* __restrict__ out1, int parts, int d) {
+  // blockIdx.y picks the array (dgamma partials / dbeta partials): one launch folds both
+  const float* in = blockIdx.y == 0 ? in0 : in1;
+  TOut* out = blockIdx.y == 0 ? out0 : out1;
   __shared__ float red[8][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
@@ -286,7 +291,7 @@ __global__ void column_sum_kernel(const float* __restrict__ in, float* __restric
     float t = 0.f;
 #pragma unroll
     for (int y = 0; y < 8; ++y) t += red[y][threadIdx.x];
-    out[c] = t;
+    out[c] = float_to_elem<TOut>(t);
   }
 }
 
@@ -326,7 +331,8 @@ std::vector<at::Tensor> layer_norm_fwd(const at::Tensor& x, const at::Tensor& ga
 }
 
 std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
-                                       const at::Tensor& mean, const at::Tensor& rstd, const c10::optional<at::Tensor>& dres) {
+                                       const at::Tensor& mean, const at::Tensor& rstd, const c10::optional<at::Tensor>& dres,
+                                       const c10::optional<at::Tensor>& dgamma_out, const c10::optional<at::Tensor>& dbeta_out) {
   TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && x.is_contiguous() && gamma.is_contiguous(), "layer_norm_bwd: contiguous CUDA tensors");
   TORCH_CHECK(dy.scalar_type() == x.scalar_type(), "dy and x must share a dtype");
   if (dres.has_value())
@@ -336,9 +342,22 @@ std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x
   const int d = static_cast<int>(x.size(-1));
   const long long rows = x.numel() / d;
   auto dx = at::empty_like(x);
-  auto dgamma = at::zeros({d}, x.options().dtype(at::kFloat));
-  auto dbeta = at::zeros({d}, x.options().dtype(at::kFloat));
-  if (rows == 0) return {dx, dgamma, dbeta};
+  TORCH_CHECK(dgamma_out.has_value() == dbeta_out.has_value(), "layer_norm_bwd: give both gradient outputs or neither");
+  at::Tensor dgamma, dbeta;
+  if (dgamma_out.has_value()) {
+    dgamma = *dgamma_out;
+    dbeta = *dbeta_out;
+    TORCH_CHECK(dgamma.is_cuda() && dgamma.is_contiguous() && dbeta.is_contiguous() && dgamma.numel() == d && dbeta.numel() == d &&
+                    dgamma.scalar_type() == dbeta.scalar_type(), "layer_norm_bwd: gradient outputs must be contiguous [d] tensors of one dtype");
+  } else {
+    dgamma = at::empty({d}, x.options().dtype(at::kFloat));
+    dbeta = at::empty({d}, x.options().dtype(at::kFloat));
+  }
+  if (rows == 0) {
+    dgamma.zero_();
+    dbeta.zero_();
+    return {dx, dgamma, dbeta};
+  }
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   const int grid = static_cast<int>(std::min<long long>((rows + LN_WARPS - 1) / LN_WARPS, 4LL * sms));
@@ -363,9 +382,18 @@ std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x
     else launch(ln_bwd_kernel<scalar_t, 1>);
   });
   NT_KERNEL_CHECK();
-  column_sum_kernel<<<(d + 31) / 32, dim3(32, 8), 0, stream>>>(part_g.data_ptr<float>(), dgamma.data_ptr<float>(), grid, d);
-  NT_KERNEL_CHECK();
-  column_sum_kernel<<<(d + 31) / 32, dim3(32, 8), 0, stream>>>(part_b.data_ptr<float>(), dbeta.data_ptr<float>(), grid, d);
+  const dim3 fold_grid((d + 31) / 32, 2);
+  if (dgamma.scalar_type() == at::kFloat) {
+    column_sum_kernel<float><<<fold_grid, dim3(32, 8), 0, stream>>>(part_g.data_ptr<float>(), part_b.data_ptr<float>(), dgamma.data_ptr<float>(),
+                                                                    dbeta.data_ptr<float>(), grid, d);
+  } else if (dgamma.scalar_type() == at::kBFloat16) {
+    column_sum_kernel<c10::BFloat16><<<fold_grid, dim3(32, 8), 0, stream>>>(part_g.data_ptr<float>(), part_b.data_ptr<float>(),
+                                                                            dgamma.data_ptr<c10::BFloat16>(), dbeta.data_ptr<c10::BFloat16>(), grid, d);
+  } else {
+    TORCH_CHECK(dgamma.scalar_type() == at::kHalf, "layer_norm_bwd: gradient outputs must be fp32, bf16 or fp16");
+    column_sum_kernel<c10::Half><<<fold_grid, dim3(32, 8), 0, stream>>>(part_g.data_ptr<float>(), part_b.data_ptr<float>(),
+                                                                        dgamma.data_ptr<c10::Half>(), dbeta.data_ptr<c10::Half>(), grid, d);
+  }
   NT_KERNEL_CHECK();
   return {dx, dgamma, dbeta};
 }

@@ -46,10 +46,14 @@ at::Tensor bwd_grouped_gemm_dW_kernel(const at::Tensor& X, const at::Tensor& off
 // ---- normalisation, loss, optimizer
 std::vector<at::Tensor> layer_norm_fwd(const at::Tensor& x, const at::Tensor& gamma, const at::Tensor& beta, double eps);
 // `dres` (optional, shaped like x): a gradient that reached x on a path around the normalisation
-// (the residual connection); it is added to dx in the same pass.
+// (the residual connection); it is added to dx in the same pass.  `dgamma_out` / `dbeta_out`
+// (optional, [d], fp32 or a 16-bit dtype): where to write the parameter gradients; without them
+// two fp32 tensors are allocated.
 std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gamma,
                                        const at::Tensor& mean, const at::Tensor& rstd,
-                                       const c10::optional<at::Tensor>& dres);
+                                       const c10::optional<at::Tensor>& dres,
+                                       const c10::optional<at::Tensor>& dgamma_out,
+                                       const c10::optional<at::Tensor>& dbeta_out);
 at::Tensor cross_entropy_fwd_bwd(at::Tensor logits, const at::Tensor& targets, int64_t V, double grad_scale, bool write_grad);
 at::Tensor adamw_step(at::Tensor param, const at::Tensor& grad, at::Tensor master, at::Tensor m, at::Tensor v, int64_t step,
                       double lr, double beta1, double beta2, double eps, double wd, double grad_scale, bool want_sq);

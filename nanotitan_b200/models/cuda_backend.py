@@ -20,6 +20,39 @@ from nanotitan_b200.models.utils import ModelShardSpec, MoELayerStats
 from nanotitan_b200.profiler import nvtx_range
 
 
+_CONSTANTS: dict = {}
+
+
+def _single_expert_constants(device, assignments: int, alpha: float):
+    """(counts int32 [1], ones fp32 [1], alpha fp32 scalar) for a one-expert layer, made once per device."""
+    key = (device, assignments, alpha)
+    hit = _CONSTANTS.get(key)
+    if hit is None:
+        hit = (
+            torch.full((1,), assignments, dtype=torch.int32, device=device),
+            torch.ones(1, dtype=torch.float32, device=device),
+            torch.full((), alpha, dtype=torch.float32, device=device),
+        )
+        _CONSTANTS[key] = hit
+    return hit
+
+
+class _ZeroGradLink(torch.autograd.Function):
+    """Returns the constant `value` while keeping `weight` in the graph with an exactly-zero gradient."""
+
+    @staticmethod
+    def forward(ctx, weight, value):
+        ctx.weight = weight
+        return value.view_as(value)
+
+    @staticmethod
+    def backward(ctx, _grad):
+        from nanotitan_b200.ops import native
+
+        dw = native.grad_buffer(ctx.weight)
+        return dw.zero_(), None
+
+
 class CUDAMoEBackend:
     def __init__(self, cfg, experts: nn.Module, router: nn.Linear, spec: ModelShardSpec | None = None):
         self.cfg, self.router, self.experts = cfg, router, experts
@@ -41,9 +74,13 @@ class CUDAMoEBackend:
             offsets = native.whole_segment(tokens, flat.device)
             with nvtx_range("moe/expert_compute"):
                 out = native.swiglu_experts(flat, self.experts.W_gate, self.experts.W_val, self.experts.W_out, offsets, res)
-            counts = torch.full((1,), tokens * self.cfg.top_k, dtype=torch.int32, device=flat.device)
-            # keeps the router weight in the graph with an exactly-zero gradient, as softmax over one logit gives
-            probs_mean = torch.ones(1, dtype=torch.float32, device=flat.device) + 0.0 * self.router.weight.float().sum()
+            # Routing statistics are constants here (fraction 1, probability 1); the loss is tied to
+            # the router weight by a node whose backward is one zero-fill, which is the gradient
+            # softmax over a single logit gives.
+            counts, ones, alpha = _single_expert_constants(flat.device, tokens * self.cfg.top_k, float(self.cfg.router_alpha))
+            aux = _ZeroGradLink.apply(self.router.weight, alpha) if self.router.weight.requires_grad else alpha
+            stats = MoELayerStats.single_expert(self.cfg, counts, ones, aux)
+            return out.reshape(batch, seq_len, d_model), stats
         elif self.spec.ep_size > 1:
             from nanotitan_b200.parallel.ep import expert_parallel_moe
 

@@ -74,6 +74,21 @@ class MoELayerStats:
     cfg: Any
     aux_loss: torch.Tensor | None = None
 
+    @classmethod
+    def single_expert(cls, cfg, tokens_per_expert, ones, aux_loss):
+        """Statistics of a layer with one expert, where every quantity is known without arithmetic:
+        fraction 1, mean probability 1, loss alpha * 1 * (1 * 1).  The caller passes cached
+        constants (`ones` is a float [1] tensor of 1.0), so no kernel runs."""
+        stats = object.__new__(cls)
+        stats.tokens_per_expert = tokens_per_expert
+        stats.probs_per_expert = ones
+        stats.cfg = cfg
+        stats.num_tokens = None
+        stats.total_assignments = tokens_per_expert.sum() if tokens_per_expert.numel() != 1 else tokens_per_expert[0]
+        stats.ass_frac_per_expert = ones
+        stats.aux_loss = aux_loss
+        return stats
+
     def __post_init__(self) -> None:
         if self.probs_per_expert.ndim == 2:
             self.num_tokens = self.probs_per_expert.shape[0]

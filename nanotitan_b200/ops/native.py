@@ -149,19 +149,30 @@ def linear(x, w, residual=None):
 
 
 # ------------------------------------------------------------------------------- layer norm
+def _ln_backward(ctx, dy, x, gamma, mean, rstd, dres):
+    """(dx, dgamma, dbeta); the parameter gradients are folded straight into the parameters' dtype
+    and, on a step's first gradient, into their slots of the gradient bucket."""
+    gamma_p, beta_p = ctx.params
+    dg, db = grad_buffer(gamma_p), grad_buffer(beta_p)
+    if not (dg.is_contiguous() and db.is_contiguous()):
+        dg, db = torch.empty_like(gamma_p), torch.empty_like(beta_p)
+    dx, dg, db = get_ext().layer_norm_bwd(dy.contiguous(), x, gamma.contiguous(), mean, rstd, dres, dg, db)
+    return dx, dg, db
+
+
 class _LayerNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, gamma, beta, eps):
         xc = x.contiguous()
         y, mean, rstd = get_ext().layer_norm_fwd(xc, gamma.contiguous(), beta.contiguous(), eps)
         ctx.save_for_backward(xc, gamma, mean, rstd)
+        ctx.params = (gamma, beta)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, gamma, mean, rstd = ctx.saved_tensors
-        dx, dgamma, dbeta = get_ext().layer_norm_bwd(dy.contiguous(), x, gamma.contiguous(), mean, rstd)
-        return dx, dgamma.to(gamma.dtype), dbeta.to(gamma.dtype), None
+        return (*_ln_backward(ctx, dy, x, gamma, mean, rstd, None), None)
 
 
 def layer_norm(x, gamma, beta, eps=1e-8):
@@ -181,6 +192,7 @@ class _LayerNormResidual(torch.autograd.Function):
         xc = x.contiguous()
         y, mean, rstd = get_ext().layer_norm_fwd(xc, gamma.contiguous(), beta.contiguous(), eps)
         ctx.save_for_backward(xc, gamma, mean, rstd)
+        ctx.params = (gamma, beta)
         return y, xc.view_as(xc)
 
     @staticmethod
@@ -189,8 +201,7 @@ class _LayerNormResidual(torch.autograd.Function):
         if dy is None:
             return dpass, None, None, None
         dres = None if dpass is None else dpass.contiguous()
-        dx, dgamma, dbeta = get_ext().layer_norm_bwd(dy.contiguous(), x, gamma.contiguous(), mean, rstd, dres)
-        return dx, dgamma.to(gamma.dtype), dbeta.to(gamma.dtype), None
+        return (*_ln_backward(ctx, dy, x, gamma, mean, rstd, dres), None)
 
 
 def layer_norm_residual(x, gamma, beta, eps=1e-8):
