@@ -295,6 +295,13 @@ void gemm_tc(const at::Tensor& A, bool a_mn, const std::vector<at::Tensor>& Bs, 
   }
 
   if (args.M == 0 || args.N == 0) return;
+  if (mode == gemm::kGroupedK && a_rows == 0) {
+    // An empty reduction (an expert that received no token this step): the products are zero.
+    // A tensor map cannot describe a tensor without rows, so this case never reaches the kernel.
+    if (!accumulate)
+      for (const auto& c : Cs) c.zero_();
+    return;
+  }
 
   // ---- staged TMA stores of the epilogue (16-bit outputs of the dense and grouped-M shapes)
   CUtensorMap tC[3];

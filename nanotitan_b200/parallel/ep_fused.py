@@ -101,6 +101,11 @@ class FusedExchange:
         local_offsets[1:] = torch.cumsum(per_expert, dim=0)
         received = int(local_offsets[-1].item())  # the layer's one host read
         assignments = packed_x.shape[0]
+        if not 0 <= received <= self.ep * assignments:
+            raise RuntimeError(
+                f"expert-parallel count exchange returned {received} rows for rank {self.rank}; at most "
+                f"{self.ep * assignments} can arrive (count matrix: {cmat.tolist()})"
+            )
         expert_in = _Push.apply(packed_x, self, cmat, 0, assignments, received)
         return expert_in, local_offsets, (cmat, assignments)
 

@@ -88,7 +88,7 @@ def _offsets(counts):
     return off.cuda()
 
 
-@pytest.mark.parametrize("counts", [[128, 128], [3, 1, 4], [0, 300, 0, 77, 129], [513]])
+@pytest.mark.parametrize("counts", [[128, 128], [3, 1, 4], [0, 300, 0, 77, 129], [513], [0], [0, 0]])
 def test_grouped_forward_dgrad_wgrad(counts):
     ext = _ext()
     torch.manual_seed(3)
@@ -108,6 +108,23 @@ def test_grouped_forward_dgrad_wgrad(counts):
         torch.testing.assert_close(dx[lo : lo + c].float(), ds @ w[e].float().t(), rtol=2e-2, atol=0.1)
         torch.testing.assert_close(dw[e].float(), xs.t() @ ds, rtol=2e-2, atol=0.02 * max(c, 1) ** 0.5 + 1e-3)
         lo += c
+
+
+def test_expert_without_tokens_gets_zero_gradients():
+    """A rank whose only local expert received no token this step: empty forward, zero weight gradients."""
+    from nanotitan_b200.ops import native
+
+    d, f = 128, 256
+    x = torch.empty(0, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    wg, wv = (_rand(1, d, f, scale=0.1).requires_grad_() for _ in range(2))
+    wo = _rand(1, f, d, scale=0.1).requires_grad_()
+    off = _offsets([0])
+    y = native.swiglu_experts(x, wg, wv, wo, off)
+    assert y.shape == (0, d)
+    y.sum().backward()
+    for w in (wg, wv, wo):
+        assert w.grad is not None and torch.count_nonzero(w.grad) == 0
+    _status_clean()
 
 
 def test_split_sources_and_destinations():
