@@ -133,7 +133,7 @@ def bench_moe(iters):
         w = torch.randn(E, d, device="cuda") * 0.1
         ms = timed(lambda: ext.router_topk(x, w, k), iters)
         report(f"router_topk T{T} d{d} E{E} k{k}", ms, nbytes=T * d * 2 + T * E * 4)
-        gates, idx, probs, counts = ext.router_topk(x, w, k)
+        gates, idx, probs, counts = ext.router_topk(x, w, k)[:4]
         ms = timed(lambda: ext.assign_slots(idx, counts), iters)
         report(f"assign_slots T{T} E{E} k{k}", ms, nbytes=T * k * 8)
         offsets, slot_of = ext.assign_slots(idx, counts)

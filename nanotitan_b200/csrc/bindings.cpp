@@ -43,6 +43,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cross_entropy_fwd_bwd", &nt::cross_entropy_fwd_bwd);
   m.def("adamw_step", &nt::adamw_step);
   m.def("router_topk", &nt::router_topk);
+  m.def("router_bwd", &nt::router_bwd);
   m.def("assign_slots", &nt::assign_slots);
   m.def("pack_fwd", &nt::pack_fwd);
   m.def("combine_fwd", &nt::combine_fwd);

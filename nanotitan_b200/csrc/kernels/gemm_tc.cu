@@ -27,6 +27,7 @@ int dtype_code(const at::Tensor& t) {
 void check_operand(const at::Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
   TORCH_CHECK(t.dim() == 2 || t.dim() == 3, name, " must be 2-D or 3-D");
+  if (t.numel() == 0) return;  // an operand without rows never reaches a kernel; its strides mean nothing
   TORCH_CHECK(t.stride(-1) == 1, name, " must have a contiguous last dim");
   TORCH_CHECK(t.stride(-2) % 8 == 0, name, ": row stride must be a multiple of 8 elements (TMA needs 16-byte strides)");
   TORCH_CHECK(reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, name, " must be 16-byte aligned");

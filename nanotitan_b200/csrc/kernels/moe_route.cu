@@ -28,10 +28,14 @@ constexpr int RT_SLOTS = RT_MAX_E / 32;
 template <typename T, typename WT>
 __global__ void __launch_bounds__(RT_WARPS * 32)
 router_topk_kernel(const T* __restrict__ x, const WT* __restrict__ w, float* __restrict__ gates, int* __restrict__ idx,
-                   float* __restrict__ probs, int* __restrict__ counts,
+                   float* __restrict__ probs, int* __restrict__ counts, float* __restrict__ prob_parts,
                    long long tokens, int d, int E, int k) {
   extern __shared__ float sx[];  // [RT_WARPS][RT_TOK][d] token rows as fp32
   __shared__ int s_counts[RT_MAX_E];
+  __shared__ float s_psum[RT_WARPS][RT_MAX_E];
+  float psum[RT_SLOTS];  // this warp's running sum of the probabilities of expert (slot * 32 + lane)
+#pragma unroll
+  for (int s = 0; s < RT_SLOTS; ++s) psum[s] = 0.f;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int e = threadIdx.x; e < E; e += blockDim.x) s_counts[e] = 0;
   __syncthreads();
@@ -89,6 +93,7 @@ router_topk_kernel(const T* __restrict__ x, const WT* __restrict__ w, float* __r
 #pragma unroll
       for (int s = 0; s < RT_SLOTS; ++s) {
         p[s] *= inv;
+        psum[s] += p[s];
         const int e = s * 32 + lane;
         if (e < E) probs[tok * E + e] = p[s];
       }
@@ -124,9 +129,85 @@ router_topk_kernel(const T* __restrict__ x, const WT* __restrict__ w, float* __r
     }
     __syncwarp();
   }
+#pragma unroll
+  for (int s = 0; s < RT_SLOTS; ++s)
+    if (s * 32 + lane < E) s_psum[warp][s * 32 + lane] = psum[s];
   __syncthreads();
-  for (int e = threadIdx.x; e < E; e += blockDim.x)
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
     if (s_counts[e] != 0) atomicAdd(&counts[e], s_counts[e]);
+    float t = 0.f;  // warps in index order: the block's partial sum does not depend on scheduling
+#pragma unroll
+    for (int w2 = 0; w2 < RT_WARPS; ++w2) t += s_psum[w2][e];
+    prob_parts[static_cast<long long>(blockIdx.x) * E + e] = t;
+  }
+}
+
+// out[c] = scale * sum over `parts` rows of in[p][c]; 8 row groups per column, added in a fixed order.
+__global__ void scaled_column_sum_kernel(const float* __restrict__ in, float* __restrict__ out, int parts, int cols, float scale) {
+  __shared__ float red[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  float s = 0.f;
+  if (c < cols)
+    for (int p = threadIdx.y; p < parts; p += 8) s += in[static_cast<long long>(p) * cols + c];
+  red[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int y = 0; y < 8; ++y) t += red[y][threadIdx.x];
+    out[c] = t * scale;
+  }
+}
+
+// Backward of softmax -> top-k -> renormalise, one thread per token.
+//   dl_tok = gradient of the logits through the gates (reaches tokens and router weight);
+//   dl_all = dl_tok + gradient through the probabilities themselves (load-balancing loss; router weight only).
+// The probability gradient may come as a [T, E] tensor, as the gradient of the column means ([E], every
+// token then gets d_mean[e] / T), both, or neither.
+template <typename TOut>
+__global__ void router_bwd_kernel(const float* __restrict__ gates, const int* __restrict__ idx, const float* __restrict__ probs,
+                                  const float* __restrict__ dgates, const float* __restrict__ dprobs,
+                                  const float* __restrict__ dprobs_mean, TOut* __restrict__ dl_tok, TOut* __restrict__ dl_all,
+                                  long long tokens, int E, int k) {
+  const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= tokens) return;
+  const float* p = probs + t * E;
+  const int* id = idx + t * k;
+  float top_sum = 0.f, gd = 0.f;
+  for (int j = 0; j < k; ++j) {
+    top_sum += p[id[j]];
+    if (dgates != nullptr) gd += dgates[t * k + j] * gates[t * k + j];
+  }
+  // d(prob of chosen expert j) and its dot product with the probabilities
+  float dot = 0.f;
+  if (dgates != nullptr)
+    for (int j = 0; j < k; ++j) dot += (dgates[t * k + j] - gd) / top_sum * p[id[j]];
+  const float inv_t = 1.f / static_cast<float>(tokens);
+  float dot2 = 0.f;
+  const bool aux = dprobs != nullptr || dprobs_mean != nullptr;
+  if (aux)
+    for (int e = 0; e < E; ++e) {
+      float g = 0.f;
+      if (dprobs != nullptr) g += dprobs[t * E + e];
+      if (dprobs_mean != nullptr) g += dprobs_mean[e] * inv_t;
+      dot2 += g * p[e];
+    }
+  for (int e = 0; e < E; ++e) {
+    float dp = 0.f;
+    if (dgates != nullptr)
+      for (int j = 0; j < k; ++j)
+        if (id[j] == e) dp = (dgates[t * k + j] - gd) / top_sum;
+    const float tok = p[e] * (dp - dot);
+    float all = tok;
+    if (aux) {
+      float g = 0.f;
+      if (dprobs != nullptr) g += dprobs[t * E + e];
+      if (dprobs_mean != nullptr) g += dprobs_mean[e] * inv_t;
+      all += p[e] * (g - dot2);
+    }
+    dl_tok[t * E + e] = float_to_elem<TOut>(tok);
+    dl_all[t * E + e] = float_to_elem<TOut>(all);
+  }
 }
 
 // Block e: offsets by a serial scan of `counts`, then slot_of[a] for every assignment a routed to e.
@@ -204,7 +285,7 @@ __global__ void count_experts_kernel(const int* __restrict__ topk, const int* __
 
 }  // namespace
 
-// -> gates [T,k] f32, idx [T,k] i32, probs [T,E] f32, counts [E] i32
+// -> gates [T,k] f32, idx [T,k] i32, probs [T,E] f32, counts [E] i32, probs_mean [E] f32 (column means of probs)
 std::vector<at::Tensor> router_topk(const at::Tensor& x, const at::Tensor& w, int64_t k) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous() && w.is_contiguous() && w.dim() == 2, "router_topk: x [T,d], w [E,d], contiguous");
   TORCH_CHECK(w.size(1) == x.size(1), "router_topk: width mismatch");
@@ -222,7 +303,9 @@ std::vector<at::Tensor> router_topk(const at::Tensor& x, const at::Tensor& w, in
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   const long long per_block = RT_WARPS * RT_TOK;
   const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>((tokens + per_block - 1) / per_block, 8LL * sms)));
+  auto probs_mean = tokens > 0 ? at::empty({E}, f32) : at::zeros({E}, f32);
   if (tokens > 0) {
+    auto parts = at::empty({grid, E}, f32);
     const size_t smem = sizeof(float) * RT_WARPS * RT_TOK * d;
     TORCH_CHECK(smem <= 160 * 1024, "router_topk: d too large");
     cudaStream_t stream = at::cuda::getCurrentCUDAStream();
@@ -232,12 +315,46 @@ std::vector<at::Tensor> router_topk(const at::Tensor& x, const at::Tensor& w, in
         auto kernel = router_topk_kernel<x_t, scalar_t>;
         if (smem > 48 * 1024) NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         kernel<<<grid, RT_WARPS * 32, smem, stream>>>(x.data_ptr<x_t>(), w.data_ptr<scalar_t>(), gates.data_ptr<float>(), idx.data_ptr<int>(),
-            probs.data_ptr<float>(), counts.data_ptr<int>(), tokens, d, E, static_cast<int>(k));
+            probs.data_ptr<float>(), counts.data_ptr<int>(), parts.data_ptr<float>(), tokens, d, E, static_cast<int>(k));
       });
     });
     NT_KERNEL_CHECK();
+    scaled_column_sum_kernel<<<(E + 31) / 32, dim3(32, 8), 0, stream>>>(parts.data_ptr<float>(), probs_mean.data_ptr<float>(), grid, E,
+                                                                         1.f / static_cast<float>(tokens));
+    NT_KERNEL_CHECK();
   }
-  return {gates, idx, probs, counts};
+  return {gates, idx, probs, counts, probs_mean};
+}
+
+// Backward of the fused router up to the logits; see router_bwd_kernel.  `like` gives the output dtype.
+std::vector<at::Tensor> router_bwd(const at::Tensor& gates, const at::Tensor& idx, const at::Tensor& probs,
+                                   const c10::optional<at::Tensor>& dgates, const c10::optional<at::Tensor>& dprobs,
+                                   const c10::optional<at::Tensor>& dprobs_mean, const at::Tensor& like) {
+  TORCH_CHECK(gates.is_cuda() && gates.is_contiguous() && gates.scalar_type() == at::kFloat && idx.is_contiguous() &&
+                  idx.scalar_type() == at::kInt && probs.is_contiguous() && probs.scalar_type() == at::kFloat,
+              "router_bwd: gates f32 [T,k], idx i32 [T,k], probs f32 [T,E], contiguous");
+  c10::cuda::CUDAGuard guard(probs.device());
+  const long long tokens = probs.size(0);
+  const int E = static_cast<int>(probs.size(1)), k = static_cast<int>(gates.size(1));
+  auto check = [&](const c10::optional<at::Tensor>& t, long long n, const char* name) -> const float* {
+    if (!t.has_value()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == at::kFloat && t->numel() == n, "router_bwd: bad ", name);
+    return t->data_ptr<float>();
+  };
+  const float* dg = check(dgates, tokens * k, "dgates");
+  const float* dp = check(dprobs, tokens * E, "dprobs");
+  const float* dm = check(dprobs_mean, E, "dprobs_mean");
+  auto dl_tok = at::empty({tokens, E}, like.options());
+  auto dl_all = at::empty({tokens, E}, like.options());
+  if (tokens == 0) return {dl_tok, dl_all};
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  const unsigned grid = static_cast<unsigned>((tokens + 127) / 128);
+  NT_DISPATCH_FLOAT(like.scalar_type(), "router_bwd", [&] {
+    router_bwd_kernel<scalar_t><<<grid, 128, 0, stream>>>(gates.data_ptr<float>(), idx.data_ptr<int>(), probs.data_ptr<float>(), dg, dp, dm,
+                                                          dl_tok.data_ptr<scalar_t>(), dl_all.data_ptr<scalar_t>(), tokens, E, k);
+  });
+  NT_KERNEL_CHECK();
+  return {dl_tok, dl_all};
 }
 
 // -> offsets [E+1] i32, slot_of [T,k] i32

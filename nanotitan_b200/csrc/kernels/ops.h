@@ -79,6 +79,9 @@ void ep_push_rows(const at::Tensor& src, const at::Tensor& dst_peers, int64_t ds
 
 // ---- MoE routing / dispatch
 std::vector<at::Tensor> router_topk(const at::Tensor& x, const at::Tensor& w, int64_t k);
+std::vector<at::Tensor> router_bwd(const at::Tensor& gates, const at::Tensor& idx, const at::Tensor& probs,
+                                   const c10::optional<at::Tensor>& dgates, const c10::optional<at::Tensor>& dprobs,
+                                   const c10::optional<at::Tensor>& dprobs_mean, const at::Tensor& like);
 std::vector<at::Tensor> assign_slots(const at::Tensor& idx, const at::Tensor& counts);
 at::Tensor count_expert_kernel(const at::Tensor& topk, const at::Tensor& mask, int64_t E, int64_t k);
 std::vector<at::Tensor> pack_fwd(const at::Tensor& x, const at::Tensor& gates, const at::Tensor& idx, const at::Tensor& slot_of);

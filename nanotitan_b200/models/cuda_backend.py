@@ -89,13 +89,13 @@ class CUDAMoEBackend:
             from nanotitan_b200.ops import native
 
             with nvtx_range("moe/router"):
-                gates, top_e, probs, counts = native.router_topk(flat, self.router.weight, self.cfg.top_k)
+                gates, top_e, counts, probs_mean = native.router_topk_mean(flat, self.router.weight, self.cfg.top_k)
             with nvtx_range("moe/pack_tokens"):
                 packed_x, packed_gate, packed_token, _, offsets, slot_of = native.pack(flat, gates, top_e, counts)
             with nvtx_range("moe/expert_compute"):
                 expert_out = self.experts(packed_x, offsets)
             with nvtx_range("moe/combine_tokens"):
                 out = native.combine(expert_out, packed_gate, packed_token, slot_of, flat.shape[0], res)
-            probs_mean = probs.mean(dim=0)
-        stats = MoELayerStats(counts.detach(), probs_per_expert=probs_mean, cfg=self.cfg)
+        stats = MoELayerStats(counts.detach(), probs_per_expert=probs_mean, cfg=self.cfg,
+                              assignments=flat.shape[0] * self.cfg.top_k)
         return out.reshape(batch, seq_len, d_model), stats

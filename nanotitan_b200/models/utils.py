@@ -73,6 +73,9 @@ class MoELayerStats:
     probs_per_expert: torch.Tensor
     cfg: Any
     aux_loss: torch.Tensor | None = None
+    # number of (token, choice) assignments when the caller knows it on the host (tokens * top_k):
+    # the fractions are then a multiplication by a constant and the loss a single dot product
+    assignments: int | None = None
 
     @classmethod
     def single_expert(cls, cfg, tokens_per_expert, ones, aux_loss):
@@ -84,8 +87,9 @@ class MoELayerStats:
         stats.probs_per_expert = ones
         stats.cfg = cfg
         stats.num_tokens = None
-        stats.total_assignments = tokens_per_expert.sum() if tokens_per_expert.numel() != 1 else tokens_per_expert[0]
-        stats.ass_frac_per_expert = ones
+        stats.assignments = None
+        stats._total = tokens_per_expert.sum() if tokens_per_expert.numel() != 1 else tokens_per_expert[0]
+        stats._frac = ones
         stats.aux_loss = aux_loss
         return stats
 
@@ -95,12 +99,23 @@ class MoELayerStats:
             self.probs_per_expert = self.probs_per_expert.mean(dim=0)
         else:
             self.num_tokens = None
-        self.total_assignments = self.tokens_per_expert.sum()
-        self.ass_frac_per_expert = self.tokens_per_expert.float() / self.total_assignments
-        assert self.ass_frac_per_expert.shape == self.probs_per_expert.shape
-        assert self.ass_frac_per_expert.ndim == 1
-        self.aux_loss = (
-            self.cfg.router_alpha
-            * self.cfg.num_experts
-            * torch.sum(self.ass_frac_per_expert * self.probs_per_expert.float())
-        )
+        assert self.tokens_per_expert.shape == self.probs_per_expert.shape
+        assert self.tokens_per_expert.ndim == 1
+        self._total = self._frac = None
+        scale = self.cfg.router_alpha * self.cfg.num_experts
+        if self.assignments:
+            self.aux_loss = torch.dot(self.tokens_per_expert.float(), self.probs_per_expert.float()) * (scale / self.assignments)
+        else:
+            self.aux_loss = scale * torch.sum(self.ass_frac_per_expert * self.probs_per_expert.float())
+
+    @property
+    def total_assignments(self) -> torch.Tensor:
+        if self._total is None:
+            self._total = self.tokens_per_expert.sum()
+        return self._total
+
+    @property
+    def ass_frac_per_expert(self) -> torch.Tensor:
+        if self._frac is None:
+            self._frac = self.tokens_per_expert.float() / self.total_assignments
+        return self._frac

@@ -277,37 +277,42 @@ def linear_cross_entropy(x, w_unembed, targets):
 
 # ------------------------------------------------------------------------------- MoE routing
 class _Router(torch.autograd.Function):
-    """Fused fp32 router.  Outputs: gates [T,k] (grad -> x and w), ids [T,k], probs [T,E]
-    (grad -> w only: the load-balancing loss sees detached tokens), counts [E]."""
+    """Fused fp32 router.  Outputs: gates [T,k] (grad -> x and w), ids [T,k], probs [T,E] and their
+    column means [E] (grad -> w only: the load-balancing loss sees detached tokens), counts [E]."""
 
     @staticmethod
     def forward(ctx, x, w, k):
-        gates, idx, probs, counts = get_ext().router_topk(x.contiguous(), w.contiguous(), k)
+        gates, idx, probs, counts, probs_mean = get_ext().router_topk(x.contiguous(), w.contiguous(), k)
         ctx.save_for_backward(x, w, gates, idx, probs)
         ctx.mark_non_differentiable(idx, counts)
-        return gates, idx, probs, counts
+        return gates, idx, probs, counts, probs_mean
 
     @staticmethod
-    def backward(ctx, dgates, _didx, dprobs, _dcounts):
+    def backward(ctx, dgates, _didx, dprobs, _dcounts, dprobs_mean):
         x, w, gates, idx, probs = ctx.saved_tensors
-        idx64 = idx.long()
-        top_sum = probs.gather(1, idx64).sum(dim=1, keepdim=True)
-        dp_top = (dgates - (dgates * gates).sum(dim=1, keepdim=True)) / top_sum
-        dp = torch.zeros_like(probs).scatter_(1, idx64, dp_top)
-        dl_tokens = probs * (dp - (dp * probs).sum(dim=1, keepdim=True))  # reaches x and w
-        dl_all = dl_tokens
-        if dprobs is not None:
-            dl_all = dl_tokens + probs * (dprobs - (dprobs * probs).sum(dim=1, keepdim=True))
+
+        def f32(t):
+            return None if t is None else t.float().contiguous()
+
+        # softmax / top-k / renormalise backward in one kernel; the two small products stay library GEMMs
+        dl_tok, dl_all = get_ext().router_bwd(gates, idx, probs, f32(dgates), f32(dprobs), f32(dprobs_mean), x)
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = dl_tokens.to(x.dtype) @ w.to(x.dtype)
+            dx = dl_tok @ w.to(x.dtype)
         if ctx.needs_input_grad[1]:
-            dw = (dl_all.to(x.dtype).t() @ x).to(w.dtype)
+            dw = (dl_all.t() @ x).to(w.dtype)
         return dx, dw, None
 
 
 def router_topk(x, w, k):
-    return _Router.apply(x, w, k)
+    """-> gates, ids, probs, counts (see `_Router`)."""
+    return _Router.apply(x, w, k)[:4]
+
+
+def router_topk_mean(x, w, k):
+    """-> gates, ids, counts, mean router probability per expert [E] (what the load-balancing loss needs)."""
+    gates, idx, _probs, counts, probs_mean = _Router.apply(x, w, k)
+    return gates, idx, counts, probs_mean
 
 
 # ------------------------------------------------------------------------------- pack / combine

@@ -50,7 +50,7 @@ def expert_parallel_moe(backend, flat: torch.Tensor, residual: torch.Tensor | No
     Returns (out [T, d], counts [E] of this rank's routing, mean router probabilities [E])."""
     cfg = backend.cfg
     with nvtx_range("moe/router"):
-        gates, top_e, probs, counts = native.router_topk(flat, backend.router.weight, cfg.top_k)
+        gates, top_e, counts, probs_mean = native.router_topk_mean(flat, backend.router.weight, cfg.top_k)
     with nvtx_range("moe/pack_tokens"):
         packed_x, packed_gate, packed_token, _, _, slot_of = native.pack(flat, gates, top_e, counts)
     if not hasattr(backend, "fused_exchange"):
@@ -70,4 +70,4 @@ def expert_parallel_moe(backend, flat: torch.Tensor, residual: torch.Tensor | No
         returned = fused.gather_back(expert_out, ctx) if fused is not None else _nccl_return(expert_out, ctx)
     with nvtx_range("moe/combine_tokens"):
         out = native.combine(returned, packed_gate, packed_token, slot_of, flat.shape[0], residual)
-    return out, counts, probs.mean(dim=0)
+    return out, counts, probs_mean

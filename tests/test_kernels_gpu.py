@@ -141,13 +141,14 @@ def test_router_topk_matches_torch(tokens, d, E, k):
     torch.manual_seed(4)
     x = torch.randn(tokens, d, device="cuda").bfloat16()
     w = torch.randn(E, d, device="cuda") * 0.3
-    gates, idx, probs, counts = _ext().router_topk(x, w, k)
+    gates, idx, probs, counts, probs_mean = _ext().router_topk(x, w, k)
     g_ref, e_ref, p_ref = ref.router_topk(x, w, k)
     torch.testing.assert_close(probs, p_ref, rtol=1e-4, atol=1e-5)
     assert torch.equal(idx.long().sort(dim=1).values, e_ref.sort(dim=1).values)
     torch.testing.assert_close(gates.sum(1), torch.ones(tokens, device="cuda"), rtol=1e-5, atol=1e-5)
     torch.testing.assert_close(gates, g_ref, rtol=1e-4, atol=1e-5)
     assert torch.equal(counts.long(), ref.expert_counts(e_ref, E))
+    torch.testing.assert_close(probs_mean, p_ref.mean(dim=0), rtol=1e-4, atol=1e-6)
 
 
 def test_slots_are_expert_major_in_token_order():
@@ -175,6 +176,26 @@ def test_router_autograd_matches_torch():
     g_ref, _, _ = ref.router_topk(xf, wf, 2)
     _, _, p_ref = ref.router_topk(xf.detach(), wf, 2)  # the aux path sees detached tokens
     ((g_ref * gg).sum() + (p_ref * gp).sum()).backward()
+    torch.testing.assert_close(x.grad.float(), xf.grad, rtol=5e-2, atol=5e-3)
+    torch.testing.assert_close(w.grad, wf.grad, rtol=5e-2, atol=5e-2)
+
+
+@pytest.mark.parametrize("tokens,E,k", [(64, 4, 2), (300, 8, 2), (33, 16, 4)])
+def test_router_mean_probability_gradient(tokens, E, k):
+    """The load-balancing path: gradient through the per-expert mean probability plus the gate path."""
+    from nanotitan_b200.ops import native
+
+    torch.manual_seed(7)
+    x = torch.randn(tokens, 32, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(E, 32, device="cuda") * 0.3).requires_grad_()
+    gates, idx, counts, pm = native.router_topk_mean(x, w, k)
+    gg, gm = torch.randn_like(gates), torch.randn_like(pm) * 10
+    ((gates * gg).sum() + (pm * gm).sum()).backward()
+    xf, wf = x.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    g_ref, _, _ = ref.router_topk(xf, wf, k)
+    _, _, p_ref = ref.router_topk(xf.detach(), wf, k)
+    ((g_ref * gg).sum() + (p_ref.mean(dim=0) * gm).sum()).backward()
+    torch.testing.assert_close(pm, p_ref.mean(dim=0), rtol=1e-4, atol=1e-6)
     torch.testing.assert_close(x.grad.float(), xf.grad, rtol=5e-2, atol=5e-3)
     torch.testing.assert_close(w.grad, wf.grad, rtol=5e-2, atol=5e-2)
 
