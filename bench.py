@@ -97,8 +97,9 @@ def _parallelism(args) -> tuple[int, int, int, str]:
     return args.gpus, 1, 1, f"dp{args.gpus}"
 
 
-def _timed_loop(torch, dist, step_fn, n_steps: int, flush, device):
-    """K steps between barrier+sync pairs, CUDA-event timed; returns the max over ranks (ms)."""
+def _timed_loop(torch, dist, step_fn, n_steps: int, flush, device, finish_fn=None):
+    """K steps between barrier+sync pairs, CUDA-event timed; returns the max over ranks (ms).
+    `finish_fn` runs after the last step, inside the timed region (reads still outstanding)."""
     if dist.is_initialized():
         dist.barrier()
     torch.cuda.synchronize()
@@ -108,6 +109,8 @@ def _timed_loop(torch, dist, step_fn, n_steps: int, flush, device):
     for i in range(n_steps):
         flush.zero_()  # 256 MiB write: evicts the 126 MB L2 between steps
         last = step_fn(i)
+    if finish_fn is not None:
+        last = finish_fn()
     end.record()
     torch.cuda.synchronize()
     if dist.is_initialized():
@@ -162,8 +165,23 @@ def run_ours(args) -> dict:
     def device_step(i):
         return step.train_step(model, dev[i % len(dev)], optimizer, collect_metrics=False)
 
+    # End to end through the public API: token ids come from pinned host memory every step and
+    # every step's loss is read back to the host.  The read is pipelined (`collect_metrics=
+    # "deferred"`): step i's metrics are collected after step i+1 has been launched, the last
+    # step's before the timed region closes.
+    in_flight = []
+
     def api_step(i):
-        return step.train_step(model, host[i % len(host)], optimizer)["train/ce_loss"].value
+        in_flight.append(step.train_step(model, host[i % len(host)], optimizer, collect_metrics="deferred"))
+        if len(in_flight) > 1:
+            return in_flight.pop(0).result()["train/ce_loss"].value
+        return None
+
+    def api_finish():
+        loss = None
+        while in_flight:
+            loss = in_flight.pop(0).result()["train/ce_loss"].value
+        return loss
 
     for i in range(args.warmup):
         device_step(i)
@@ -174,7 +192,8 @@ def run_ours(args) -> dict:
     launches = (ext.get_ext().launch_count() - launches0) if ext.have_ext() else 0
     for i in range(min(2, args.warmup)):
         api_step(i)
-    e2e_ms, loss = _timed_loop(torch, dist, api_step, args.steps, flush, device)
+    api_finish()
+    e2e_ms, loss = _timed_loop(torch, dist, api_step, args.steps, flush, device, finish_fn=api_finish)
     clocks = sampler.stop()
     value = tokens_per_step * args.steps / (ms / 1e3)
     e2e = tokens_per_step * args.steps / (e2e_ms / 1e3)
@@ -191,7 +210,9 @@ def run_ours(args) -> dict:
                    "optimizer": "AdamW lr5e-4 wd0.1, fp32 master weights", "l2": "256 MiB flush write between steps"},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
-                "h2d_bytes_per_step": 2 * batch * seq * 8, "d2h_bytes_per_step": 8,
+                "h2d_bytes_per_step": 2 * batch * seq * 8,
+                # two losses + per-layer routing counts as fp32, plus the 16-byte kernel status word
+                "d2h_bytes_per_step": 4 * (2 + cfg.model.n_layers * cfg.model.num_experts) + 16,
                 "last_loss": loss},
         "gpu_launches": int(launches),
     }
@@ -220,8 +241,23 @@ def run_reference(args) -> dict:
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     tokens_per_step = batch * seq * dims.data_world_size
 
+    # End to end through the public API: token ids come from pinned host memory every step and
+    # every step's loss is read back to the host.  The read is pipelined (`collect_metrics=
+    # "deferred"`): step i's metrics are collected after step i+1 has been launched, the last
+    # step's before the timed region closes.
+    in_flight = []
+
     def api_step(i):
-        return step.train_step(model, host[i % len(host)], optimizer)["train/ce_loss"].value
+        in_flight.append(step.train_step(model, host[i % len(host)], optimizer, collect_metrics="deferred"))
+        if len(in_flight) > 1:
+            return in_flight.pop(0).result()["train/ce_loss"].value
+        return None
+
+    def api_finish():
+        loss = None
+        while in_flight:
+            loss = in_flight.pop(0).result()["train/ce_loss"].value
+        return loss
 
     for i in range(args.warmup):
         api_step(i)

@@ -51,6 +51,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("pack_bwd", &nt::pack_bwd);
   m.def("bounded_wait_probe", &nt::bounded_wait_probe, "Let a bounded device wait run out; returns the number of threads that gave up");
   m.def("read_status", &nt::read_status, py::arg("clear") = true, "[code, kernel, detail, count] of the device status word");
+  m.def("status_word_tensor", &nt::status_word_tensor);
   m.def("launch_count", [] { return static_cast<long long>(nt::launch_counter().load()); },
         "Kernels of this library launched by this process");
 }

@@ -180,6 +180,14 @@ std::vector<int64_t> read_status(bool clear) {
   return {host.code, host.kernel, host.detail, host.count};
 }
 
+// The device's status word as a [4] int32 CUDA tensor (code, kernel, detail, count), so that a caller can read
+// it with a stream-ordered copy of its own instead of the synchronising `read_status`.
+at::Tensor status_word_tensor() {
+  int dev = 0;
+  NT_CUDA_CHECK(cudaGetDevice(&dev));
+  return at::from_blob(device_status_word(), {4}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, dev));
+}
+
 // See ops.h for the contract.
 void gemm_tc(const at::Tensor& A, bool a_mn, const std::vector<at::Tensor>& Bs, bool b_mn, int64_t b_split,
              const std::vector<at::Tensor>& Cs, int64_t mode, const c10::optional<at::Tensor>& offsets,

@@ -11,7 +11,8 @@ namespace nt {
 
 // ---- device status (bounded waits, checked indices)
 StatusWord* device_status_word();
-std::vector<int64_t> read_status(bool clear);  // [code, kernel, detail, count]
+std::vector<int64_t> read_status(bool clear);
+at::Tensor status_word_tensor();  // [code, kernel, detail, count]
 
 int64_t bounded_wait_probe(double limit_ms);  // probe.cu: makes a bounded device wait run out, on purpose
 

@@ -51,6 +51,20 @@ class _Clock:
         return b - a
 
 
+class PendingMetrics:
+    """Metrics of a step whose device-to-host copies are still in flight (see `train_step`)."""
+
+    def __init__(self, owner, model, host_f, status, done, clock, host_start, n_mb, n_local):
+        self.owner, self.model, self.host_f, self.status, self.done = owner, model, host_f, status, done
+        self.clock, self.host_start, self.n_mb, self.n_local = clock, host_start, n_mb, n_local
+        self._metrics = None
+
+    def result(self) -> dict:
+        if self._metrics is None:
+            self._metrics = self.owner._finish_metrics(self)
+        return self._metrics
+
+
 class PipelineParallel:
     def __init__(self, cfg, dim, reducers: dict):
         self.cfg = cfg
@@ -117,8 +131,12 @@ class PipelineParallel:
 
     # ------------------------------------------------------------------ step
     def train_step(self, model, batch, optimizer, collect_metrics: bool = True):
-        """One optimizer step.  `collect_metrics=False` skips the host read of the losses and the
-        end-of-step device sync (the step is still complete on the stream) and returns None."""
+        """One optimizer step.  `collect_metrics=True` returns the metrics dict (one device sync).
+        `collect_metrics=False` skips the host read and the sync (the step is still complete on the
+        stream) and returns None.  `collect_metrics="deferred"` returns a `PendingMetrics` at once:
+        the losses, routing counts and kernel status travel to pinned host memory behind the step,
+        and `.result()` waits for that step alone - call it after launching the next step and the
+        host never stalls the device."""
         x, y = batch
         n_mb = self.cfg.runtime.num_microbatches
         microbatch_x, microbatch_y = self.prepare_microbatch(x, y)
@@ -182,30 +200,61 @@ class PipelineParallel:
         self._pending = []
         if not collect_metrics:
             return None
+        pending = self._start_metrics(model, ce_losses, aux_losses, stats_list, clock, host_start, n_mb)
+        return pending if collect_metrics == "deferred" else pending.result()
 
-        # One host read for all loss values (also the step's only device sync).
-        if last:
-            ce_sum = torch.stack([c.detach().float() for c in ce_losses]).sum()
-            aux_sum = torch.stack([a.detach().float() for a in aux_losses]).sum()
-            ce_sum, aux_sum = torch.stack([ce_sum, aux_sum]).tolist()
+    def _start_metrics(self, model, ce_losses, aux_losses, stats_list, clock, host_start, n_mb) -> "PendingMetrics":
+        """Pack everything the step's metrics need from the device (losses, routing counts, the
+        kernels' status word) into two stream-ordered copies to pinned host memory."""
+        last = self.dim.is_pp_last_stage
+        zero = torch.zeros((), dtype=torch.float32, device=self.device)
+        ce_sum = torch.stack([c.detach().float() for c in ce_losses]).sum() if last else zero
+        aux_sum = torch.stack([a.detach().float() for a in aux_losses]).sum() if last else zero
+        n_local = len(stats_list[0]) if stats_list and stats_list[0] else 0
+        parts = [ce_sum.reshape(1), aux_sum.reshape(1)]
+        if n_local:
+            counts = torch.stack(
+                [torch.stack([mb[i].tokens_per_expert.detach().float() for i in range(n_local)]) for mb in stats_list]
+            ).sum(dim=0)  # [local layers, E]
+            parts.append(counts.reshape(-1))
+        floats = torch.cat(parts)
+        status = None
+        if self.device.type == "cuda":
+            from nanotitan_b200.ops import ext
+
+            host_f = torch.empty(floats.shape, dtype=torch.float32, pin_memory=True)
+            host_f.copy_(floats, non_blocking=True)
+            if ext.have_ext():
+                status = torch.empty(4, dtype=torch.int32, pin_memory=True)
+                status.copy_(ext.get_ext().status_word_tensor(), non_blocking=True)
+            done = torch.cuda.Event()
+            done.record()
         else:
-            ce_sum = aux_sum = 0.0
-        self.synchronize_device()
-        self._raise_on_device_failure()
-        step_time = clock.seconds("start", "end")
+            host_f, done = floats, None
+        return PendingMetrics(self, model, host_f, status, done, clock, host_start, n_mb, n_local)
+
+    def _finish_metrics(self, pending: "PendingMetrics") -> dict:
+        if pending.done is not None:
+            pending.done.synchronize()  # this step only: later steps may already be running
+        if pending.status is not None and int(pending.status[0]) != 0:
+            self._raise_on_device_failure()
+        values = pending.host_f.tolist()
+        ce_sum, aux_sum = values[0], values[1]
+        last, n_mb, clock = self.dim.is_pp_last_stage, pending.n_mb, pending.clock
         metrics = {
             "train/ce_loss": ScalarMetric(ce_sum / n_mb, reduce="sum"),
             "train/lb_loss": ScalarMetric(aux_sum / n_mb, reduce="sum"),
             # same precedence as the reference: sum(ce) + sum(aux)/n (src/parallel/pp.py:124)
             "train/total_loss": ScalarMetric(ce_sum + aux_sum / n_mb if last else 0.0, reduce="sum"),
-            "time/step_time": ScalarMetric(step_time, reduce="max"),
+            "time/step_time": ScalarMetric(clock.seconds("start", "end"), reduce="max"),
             "time/forward_time": ScalarMetric(clock.seconds("start", "forward_end"), reduce="max"),
-            "time/backward_time": ScalarMetric(
-                clock.seconds("forward_end", "backward_end"), reduce="max"
-            ),
-            "time/host_step_time": ScalarMetric(time.perf_counter() - host_start, reduce="max"),
+            "time/backward_time": ScalarMetric(clock.seconds("forward_end", "backward_end"), reduce="max"),
+            "time/host_step_time": ScalarMetric(time.perf_counter() - pending.host_start, reduce="max"),
         }
-        metrics.update(self._moe_route_fraction_metrics(model, stats_list))
+        counts = None
+        if pending.n_local:
+            counts = pending.host_f[2:].reshape(pending.n_local, -1).clone()
+        metrics.update(self._moe_route_fraction_metrics(pending.model, counts))
         return metrics
 
     def backward(self, ce_loss, moe_aux_loss, model, microbatch_idx, incoming=None) -> None:
@@ -226,21 +275,15 @@ class PipelineParallel:
             reducer.finalize_backward()
 
     # ------------------------------------------------------------------ metrics
-    def _moe_route_fraction_metrics(self, model, moe_stats_list) -> dict:
-        """Per global layer, the fraction of assignments each expert received; stages that do
-        not own a layer contribute zeros so a SUM over ranks gives the DP mean."""
+    def _moe_route_fraction_metrics(self, model, counts) -> dict:
+        """Per global layer, the fraction of assignments each expert received (`counts`: host tensor
+        [local layers, E] or None); stages that do not own a layer contribute zeros so a SUM over
+        ranks gives the DP mean."""
         metrics = {}
         local = {}
-        if moe_stats_list and moe_stats_list[0]:
-            n_local = len(moe_stats_list[0])
-            counts = torch.stack(
-                [
-                    torch.stack([mb[i].tokens_per_expert.detach().float() for i in range(n_local)])
-                    for mb in moe_stats_list
-                ]
-            ).sum(dim=0)  # [local layers, E]
-            fracs = (counts / counts.sum(dim=1, keepdim=True).clamp_min(1.0)).cpu()
-            for i in range(n_local):
+        if counts is not None:
+            fracs = counts / counts.sum(dim=1, keepdim=True).clamp_min(1.0)
+            for i in range(fracs.shape[0]):
                 local[model.spec.layer_start + i] = fracs[i]
         # DP is folded over EP: dp*ep ranks per stage see different data.
         replicas = self.dim.dp_size * self.dim.ep_size
