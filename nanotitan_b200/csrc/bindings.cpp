@@ -14,6 +14,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("random_op", &nt::random_op, "Zero vector of length x with t's options");
   m.def("copy_scalar", &nt::copy_scalar, "Element-wise copy of n elements");
   m.def("copy_vector", &nt::copy_vector, "16-byte vector copy");
+  m.def("copy_rows_prefix", &nt::copy_rows_prefix);
   m.def("peer_copy_scalar", &nt::peer_copy_scalar, "GPU-to-GPU copy over NVLink");
   m.def("count_expert_kernel", &nt::count_expert_kernel, "Histogram of expert ids");
   m.def("pack_tokens_kernel", &nt::pack_tokens_kernel, "Pack token rows into expert-major order");

@@ -28,6 +28,16 @@ __global__ void copy_vector_kernel(const uint4* __restrict__ src, uint4* __restr
   if (blockIdx.x == 0 && threadIdx.x < tail) dst_tail[threadIdx.x] = src_tail[threadIdx.x];
 }
 
+// dst[i] = src[i] for the first rows[0] rows only; the row count lives on the device, so the host
+// launches without knowing it (rows past the count keep whatever dst held).
+__global__ void copy_rows_prefix_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const int* __restrict__ rows,
+                                        long long max_rows, long long vec_per_row) {
+  const long long n = min(static_cast<long long>(rows[0]), max_rows) * vec_per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[i] = src[i];
+}
+
 int copy_grid(long long work_items) {
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   return static_cast<int>(std::max<long long>(1, std::min<long long>((work_items + 255) / 256, 16LL * sms)));
@@ -65,6 +75,23 @@ void copy_vector(const at::Tensor& src, at::Tensor dst) {
   auto* d = static_cast<uint8_t*>(dst.data_ptr());
   copy_vector_kernel<<<copy_grid(n_vec), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
       reinterpret_cast<const uint4*>(s), reinterpret_cast<uint4*>(d), n_vec, s + n_vec * 16, d + n_vec * 16, tail);
+  NT_KERNEL_CHECK();
+}
+
+// First `rows[0]` rows of src [R, d] -> dst [>= R', d] (rows: int32 CUDA tensor with one element; rows of 16-byte multiples).
+void copy_rows_prefix(const at::Tensor& src, at::Tensor dst, const at::Tensor& rows) {
+  TORCH_CHECK(src.is_cuda() && dst.is_cuda() && src.dim() == 2 && dst.dim() == 2 && src.is_contiguous() && dst.is_contiguous() &&
+                  src.size(1) == dst.size(1) && src.scalar_type() == dst.scalar_type(), "copy_rows_prefix: contiguous [rows, d] CUDA tensors");
+  TORCH_CHECK(rows.is_cuda() && rows.scalar_type() == at::kInt && rows.numel() == 1, "copy_rows_prefix: rows must be one int32 on the device");
+  const long long row_bytes = src.size(1) * src.element_size();
+  TORCH_CHECK(row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(src.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(dst.data_ptr()) % 16 == 0,
+              "copy_rows_prefix: 16-byte aligned rows");
+  c10::cuda::CUDAGuard guard(src.device());
+  const long long max_rows = std::min<long long>(src.size(0), dst.size(0));
+  if (max_rows == 0 || row_bytes == 0) return;
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  copy_rows_prefix_kernel<<<8 * sms, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      static_cast<const uint4*>(src.data_ptr()), static_cast<uint4*>(dst.data_ptr()), rows.data_ptr<int>(), max_rows, row_bytes / 16);
   NT_KERNEL_CHECK();
 }
 

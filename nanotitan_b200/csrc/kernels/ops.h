@@ -99,6 +99,7 @@ std::vector<at::Tensor> pack_kernel_backward(const at::Tensor& dPackedX, const a
 // ---- copies and toys
 void copy_scalar(const at::Tensor& src, at::Tensor dst, int64_t n);
 void copy_vector(const at::Tensor& src, at::Tensor dst);
+void copy_rows_prefix(const at::Tensor& src, at::Tensor dst, const at::Tensor& rows);
 void peer_copy_scalar(const at::Tensor& src, at::Tensor dst);
 at::Tensor random_op(const at::Tensor& t, int64_t x);
 

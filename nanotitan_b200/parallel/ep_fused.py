@@ -40,6 +40,10 @@ class FusedExchange:
         self.E_loc = num_experts // self.ep
         self.wait_ms = float(os.environ.get("NT_COMM_WAIT_MS", "60000"))
         self.blocks = int(os.environ.get("NT_EP_BLOCKS", "96"))
+        # NT_EP_HOST_COUNTS=1: read the received row count back per layer (exact-size buffers, one
+        # host sync per layer).  Default: size the expert-side buffers for the worst case and keep
+        # the count on the device, so the host never waits inside a step.
+        self.host_counts = os.environ.get("NT_EP_HOST_COUNTS", "0") == "1"
         self._handles = {}
         self.flags = self._alloc(FLAG_WORDS, torch.int32)
         self.flags.zero_()
@@ -84,13 +88,20 @@ class FusedExchange:
                                       self.rank, self.ep, self._next_epoch(), 0, self.wait_ms)
         return self.cmat.clone()
 
-    def push(self, rows: torch.Tensor, cmat: torch.Tensor, direction: int, assignments: int, out_rows: int) -> torch.Tensor:
+    def push(self, rows: torch.Tensor, cmat: torch.Tensor, direction: int, assignments: int, out_rows: int,
+             landed: torch.Tensor | None = None) -> torch.Tensor:
+        """`landed` (int32 [1] on the device): how many rows arrive here, when `out_rows` is only the
+        worst case; the rows past it in the result are uninitialised and nobody reads them."""
         cap = self.ep * assignments if direction == 0 else assignments
         staging = self._staging_for(direction, cap, rows.shape[1], rows.dtype)
         get_ext().ep_push_rows(rows.contiguous(), self.staging_peers[direction], staging.shape[0], cmat, self.E_loc, direction,
                                self.block_counter, self.flags, self.flag_peers, self.rank, self.ep, self._next_epoch(), 0,
                                self.wait_ms, self.blocks)
-        return staging[:out_rows].clone()
+        if landed is None:
+            return staging[:out_rows].clone()
+        out = torch.empty(out_rows, rows.shape[1], dtype=rows.dtype, device=rows.device)
+        get_ext().copy_rows_prefix(staging, out, landed)
+        return out
 
     # ------------------------------------------------------------------ layer interface (see parallel/ep.py)
     def dispatch(self, packed_x: torch.Tensor, counts: torch.Tensor):
@@ -99,31 +110,41 @@ class FusedExchange:
         per_expert = mine.sum(dim=0)
         local_offsets = torch.zeros(self.E_loc + 1, dtype=torch.int32, device=packed_x.device)
         local_offsets[1:] = torch.cumsum(per_expert, dim=0)
-        received = int(local_offsets[-1].item())  # the layer's one host read
         assignments = packed_x.shape[0]
-        if not 0 <= received <= self.ep * assignments:
-            raise RuntimeError(
-                f"expert-parallel count exchange returned {received} rows for rank {self.rank}; at most "
-                f"{self.ep * assignments} can arrive (count matrix: {cmat.tolist()})"
-            )
-        expert_in = _Push.apply(packed_x, self, cmat, 0, assignments, received)
-        return expert_in, local_offsets, (cmat, assignments)
+        if self.host_counts:
+            received = int(local_offsets[-1].item())  # the layer's one host read
+            if not 0 <= received <= self.ep * assignments:
+                raise RuntimeError(
+                    f"expert-parallel count exchange returned {received} rows for rank {self.rank}; at most "
+                    f"{self.ep * assignments} can arrive (count matrix: {cmat.tolist()})"
+                )
+            landed = None
+        else:
+            # Worst case: every rank sends all its assignments here.  The grouped GEMMs walk the
+            # tiles that `local_offsets` describes, so the unused tail costs memory, not time.
+            received = self.ep * assignments
+            landed = local_offsets[-1:]
+        expert_in = _Push.apply(packed_x, self, cmat, 0, assignments, received, landed, None)
+        return expert_in, local_offsets, (cmat, assignments, landed)
 
     def gather_back(self, expert_out: torch.Tensor, ctx) -> torch.Tensor:
-        cmat, assignments = ctx
-        return _Push.apply(expert_out, self, cmat, 1, assignments, assignments)
+        cmat, assignments, landed = ctx
+        return _Push.apply(expert_out, self, cmat, 1, assignments, assignments, None, landed)
 
 
 class _Push(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, rows, exchange, cmat, direction, assignments, out_rows):
+    def forward(ctx, rows, exchange, cmat, direction, assignments, out_rows, landed, landed_back):
+        """`landed` / `landed_back`: device-side row counts of the result / of the gradient that
+        travels the other way, when their host-side sizes are worst-case bounds (else None)."""
         ctx.exchange, ctx.cmat, ctx.direction, ctx.assignments, ctx.in_rows = exchange, cmat, direction, assignments, rows.shape[0]
-        return exchange.push(rows, cmat, direction, assignments, out_rows)
+        ctx.landed_back = landed_back
+        return exchange.push(rows, cmat, direction, assignments, out_rows, landed)
 
     @staticmethod
     def backward(ctx, grad):
-        back = ctx.exchange.push(grad, ctx.cmat, 1 - ctx.direction, ctx.assignments, ctx.in_rows)
-        return back, None, None, None, None, None
+        back = ctx.exchange.push(grad, ctx.cmat, 1 - ctx.direction, ctx.assignments, ctx.in_rows, ctx.landed_back)
+        return back, None, None, None, None, None, None, None
 
 
 _EXCHANGES: dict = {}

@@ -106,3 +106,27 @@ def test_single_process_step_without_launcher_uses_fake_dims():
     assert last < first
     spec = get_model_shard_specs(fake_dims(num_experts=4, dp_size=1), cfg)
     assert spec.layer_end == cfg.model.n_layers and spec.has_unembed_head
+
+
+def test_deferred_metrics_match_immediate_ones():
+    """`collect_metrics="deferred"` returns at once; `.result()` later gives the step's own metrics."""
+    from nanotitan_b200.parallel import PipelineParallel
+    from nanotitan_b200.parallel.reducer import ReducerV1
+
+    def run(mode):
+        cfg = tiny_app_cfg()
+        seed_everything(5)
+        model = NanoTitanModel(cfg.model, full_spec(cfg.model))
+        reducers = {k: ReducerV1(v, 1, None, 1) for k, v in model.parameter_sync_groups().items()}
+        step_fn = PipelineParallel(cfg, fake_dims(num_experts=4), reducers)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-2, weight_decay=0.1)
+        out = [step_fn.train_step(model, random_batch(cfg, s), opt, collect_metrics=mode) for s in range(3)]
+        return [m.result() if mode == "deferred" else m for m in out]  # resolved only after all steps ran
+
+    now, later = run(True), run("deferred")
+    for a, b in zip(now, later):
+        assert a.keys() == b.keys()
+        assert a["train/ce_loss"].value == pytest.approx(b["train/ce_loss"].value, rel=1e-6)
+        assert a["train/lb_loss"].value == pytest.approx(b["train/lb_loss"].value, rel=1e-6)
+        key = "moe/layer_00/route_frac_dist"
+        torch.testing.assert_close(a[key].value, b[key].value)
