@@ -241,23 +241,9 @@ def run_reference(args) -> dict:
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     tokens_per_step = batch * seq * dims.data_world_size
 
-    # End to end through the public API: token ids come from pinned host memory every step and
-    # every step's loss is read back to the host.  The read is pipelined (`collect_metrics=
-    # "deferred"`): step i's metrics are collected after step i+1 has been launched, the last
-    # step's before the timed region closes.
-    in_flight = []
-
     def api_step(i):
-        in_flight.append(step.train_step(model, host[i % len(host)], optimizer, collect_metrics="deferred"))
-        if len(in_flight) > 1:
-            return in_flight.pop(0).result()["train/ce_loss"].value
-        return None
-
-    def api_finish():
-        loss = None
-        while in_flight:
-            loss = in_flight.pop(0).result()["train/ce_loss"].value
-        return loss
+        # the reference's only step API: inputs copied from the host, losses read back, every step
+        return step.train_step(model, host[i % len(host)], optimizer)["train/ce_loss"].value
 
     for i in range(args.warmup):
         api_step(i)
