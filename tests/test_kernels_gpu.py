@@ -317,3 +317,22 @@ def test_copy_kernels_and_toys():
     mask = torch.tensor([1, 0, 1], device="cuda", dtype=torch.int32)
     topk = torch.tensor([[0, 1], [1, 2], [2, 2]], device="cuda", dtype=torch.int32)
     assert ext.count_expert_kernel(topk, mask, 3, 2).tolist() == [1, 1, 2]
+
+
+# ------------------------------------------------------------------ device-bounded copy, status word
+def test_copy_rows_prefix_copies_only_the_counted_rows():
+    ext = _ext()
+    src = torch.randn(100, 64, device="cuda").bfloat16()
+    for n in (0, 1, 37, 100, 250):  # a count past the buffers is clamped
+        dst = torch.full((100, 64), -7.0, device="cuda", dtype=torch.bfloat16)
+        ext.copy_rows_prefix(src, dst, torch.tensor([n], device="cuda", dtype=torch.int32))
+        k = min(n, 100)
+        assert torch.equal(dst[:k], src[:k])
+        assert (dst[k:] == -7.0).all()
+
+
+def test_status_word_tensor_reads_the_same_word_as_read_status():
+    ext = _ext()
+    word = ext.status_word_tensor()
+    assert word.shape == (4,) and word.dtype == torch.int32 and word.is_cuda
+    assert word.tolist() == list(ext.read_status(False))
