@@ -55,4 +55,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("status_word_tensor", &nt::status_word_tensor);
   m.def("launch_count", [] { return static_cast<long long>(nt::launch_counter().load()); },
         "Kernels of this library launched by this process");
+  m.def("launch_counts", [] { return nt::launch_sites().snapshot(); },
+        "Kernel launches of this process by host entry point");
 }

@@ -9,7 +9,8 @@
 //      (the switch adds with fp32 accumulation), else plain loads from every peer's buffer - and
 //      scales by 1/N;
 //   3. with an optimizer bound it applies AdamW to its slice of the fp32 master weights and
-//      moments and broadcasts the new bf16 parameters to every replica (`multimem.st` or peer
+//      moments (the state tensors hold that slice only: optimizer state is sharded over the
+//      ranks) and broadcasts the new bf16 parameters to every replica (`multimem.st` or peer
 //      stores); without one it broadcasts the mean gradient back into every replica's bucket;
 //   4. exit barrier (last block of the grid): nobody leaves before all peers' stores into its
 //      memory are done.
@@ -42,7 +43,8 @@ struct ArArgs {
   // parameters (optimizer mode)
   uint16_t* param_mc;
   uint16_t* param_peer[AR_MAX_RANKS];
-  float *master, *m, *v;
+  float *master, *m, *v;  // state of this rank's slice: element i of the bucket is at [i - state_lo]
+  long long state_lo;
   // flags: [slot][phase (2)][AR_MAX_RANKS] uint32 in every rank's pad
   uint32_t* flag_local;
   uint32_t* flag_peer[AR_MAX_RANKS];
@@ -173,12 +175,13 @@ bucket_allreduce_kernel(const ArArgs a) {
         float w[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          float pw = a.master[i + j], mm = a.m[i + j], vv = a.v[i + j];
+          const long long s = i - a.state_lo + j;
+          float pw = a.master[s], mm = a.m[s], vv = a.v[s];
           pw *= 1.f - a.lr * a.wd;
           mm = a.beta1 * mm + (1.f - a.beta1) * g[j];
           vv = a.beta2 * vv + (1.f - a.beta2) * g[j] * g[j];
           pw -= (a.lr / a.bc1) * mm / (sqrtf(vv) * a.rsqrt_bc2 + a.eps);
-          a.master[i + j] = pw; a.m[i + j] = mm; a.v[i + j] = vv;
+          a.master[s] = pw; a.m[s] = mm; a.v[s] = vv;
           w[j] = pw;
         }
         out = pack8(w, a.dtype);
@@ -232,7 +235,14 @@ void bucket_allreduce(at::Tensor grad_local, int64_t grad_mc, const at::Tensor& 
   a.fuse_adam = master.has_value();
   if (a.fuse_adam) {
     TORCH_CHECK(m.has_value() && v.has_value() && param_peers.numel() == world, "bucket_allreduce: optimizer mode needs master, m, v and parameter peers");
-    TORCH_CHECK(master->numel() == grad_local.numel() && m->numel() == grad_local.numel() && v->numel() == grad_local.numel(), "bucket_allreduce: state length");
+    const long long n_all = grad_local.numel();
+    const long long per = ((n_all / 8 + world - 1) / world) * 8;
+    const long long lo = std::min(n_all, per * rank), hi = std::min(n_all, lo + per);
+    // state tensors cover the whole bucket or exactly this rank's slice [lo, hi)
+    const bool whole = master->numel() == n_all;
+    TORCH_CHECK((whole || master->numel() == hi - lo) && m->numel() == master->numel() && v->numel() == master->numel(),
+                "bucket_allreduce: optimizer state must have the bucket's length or the owned slice's (", hi - lo, ")");
+    a.state_lo = whole ? 0 : lo;
     const auto* pp = param_peers.data_ptr<int64_t>();
     for (int i = 0; i < world; ++i) a.param_peer[i] = reinterpret_cast<uint16_t*>(pp[i]);
     a.master = master->data_ptr<float>();

@@ -54,6 +54,11 @@ class _ZeroGradLink(torch.autograd.Function):
 
 
 class CUDAMoEBackend:
+    # False: the load-balancing loss sees detached tokens (the reference's CUDA backend); True: its
+    # gradient also reaches the tokens (the reference's torch backend) - set for loss-parity runs
+    # against that backend.
+    aux_to_tokens = False
+
     def __init__(self, cfg, experts: nn.Module, router: nn.Linear, spec: ModelShardSpec | None = None):
         self.cfg, self.router, self.experts = cfg, router, experts
         self.spec = spec if spec is not None else ModelShardSpec.full(cfg)
@@ -89,7 +94,7 @@ class CUDAMoEBackend:
             from nanotitan_b200.ops import native
 
             with nvtx_range("moe/router"):
-                gates, top_e, counts, probs_mean = native.router_topk_mean(flat, self.router.weight, self.cfg.top_k)
+                gates, top_e, counts, probs_mean = native.router_topk_mean(flat, self.router.weight, self.cfg.top_k, self.aux_to_tokens)
             with nvtx_range("moe/pack_tokens"):
                 packed_x, packed_gate, packed_token, _, offsets, slot_of = native.pack(flat, gates, top_e, counts)
             with nvtx_range("moe/expert_compute"):

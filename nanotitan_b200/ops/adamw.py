@@ -6,6 +6,12 @@ dtype (bf16 for the benchmark configs); the optimizer holds fp32 master copies a
 and rewrites the bf16 values after each step.  When bound to the data-parallel reducers it
 reuses their flat gradient buckets (gradients are views into them), so a step is one kernel
 per bucket with no gather or scatter of tensors.
+
+Buckets that the fused all-reduce engine updates (data-parallel groups of two or more GPUs) keep
+optimizer state for this rank's 1/N slice of the bucket only (ZeRO-1): the engine's kernel
+reduces that slice, applies AdamW to it and broadcasts the new bf16 values, so fp32 master
+weights and moments of the other slices never exist on this rank.  `state_dict()` stores exactly
+those slices; a checkpoint therefore resumes on the same data-parallel size and bucket plan.
 """
 from __future__ import annotations
 
@@ -22,16 +28,18 @@ class _Chunk:
         self.params, self.spans = params, spans
         self.fused_by_engine = False
         n = bucket.buffer.numel()
+        self.owned = (0, n)  # the part of the bucket whose optimizer state lives here
         if engine is not None:
             flat = engine.alloc(n, bucket.dtype, bucket.device)  # symmetric: peers write new values into it
             flat.zero_()
+            self.owned = engine.owned_slice(n)
         else:
             flat = torch.zeros(n, dtype=bucket.dtype, device=bucket.device)
         for p, (lo, hi) in zip(params, spans):
             flat[lo:hi].copy_(p.data.reshape(-1))
             p.data = flat[lo:hi].view_as(p)
         self.flat_param = flat
-        self.master = flat.float()
+        self.master = flat[self.owned[0] : self.owned[1]].float()
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
 
@@ -90,7 +98,12 @@ class FusedAdamW(torch.optim.Optimizer):
         beta1, beta2 = group["betas"]
         self._sq_parts = []
         for c in self._chunks:
-            if c.fused_by_engine and c.bucket.launched_this_step:
+            if c.fused_by_engine:
+                if not c.bucket.launched_this_step:
+                    raise RuntimeError(
+                        "a gradient bucket bound to the fused all-reduce engine was not reduced this step; its optimizer "
+                        "state is sharded over the data-parallel ranks, so the update cannot run locally (run backward "
+                        "through the reducers with backward_grad_sync set, as PipelineParallel.train_step does)")
                 c.bucket.launched_this_step = False  # updated by the all-reduce kernel already
                 continue
             grads = c.bucket.buffer
@@ -116,26 +129,54 @@ class FusedAdamW(torch.optim.Optimizer):
         return float(torch.stack(self._sq_parts).sum().sqrt().item())
 
     # ------------------------------------------------------------------ checkpoints
+    def set_master_weights(self, values: dict) -> None:
+        """Overwrite fp32 master weights (and the stored parameters) from `values`: id(param) -> tensor
+        shaped like the parameter, e.g. fp32 weights of another run.  Each rank takes what falls into
+        the slices it owns."""
+        self._ensure_layout()
+        with torch.no_grad():
+            for c in self._chunks:
+                olo, ohi = c.owned
+                for p, (lo, hi) in zip(c.params, c.spans):
+                    src = values.get(id(p))
+                    if src is None:
+                        continue
+                    flat_src = src.reshape(-1).to(device=c.master.device, dtype=torch.float32)
+                    c.flat_param[lo:hi].copy_(flat_src)
+                    a, b = max(lo, olo), min(hi, ohi)
+                    if a < b:
+                        c.master[a - olo : b - olo].copy_(flat_src[a - lo : b - lo])
+
+    def state_bytes(self) -> int:
+        """Bytes of fp32 optimizer state (master + two moments) held by this rank."""
+        self._ensure_layout()
+        return sum(3 * 4 * c.master.numel() for c in self._chunks)
+
     def state_dict(self):
         self._ensure_layout()
-        per_param = []
+        chunks = []
         for c in self._chunks:
-            for lo, hi in c.spans:
-                per_param.append({"master": c.master[lo:hi].clone().cpu(), "exp_avg": c.exp_avg[lo:hi].clone().cpu(),
-                                  "exp_avg_sq": c.exp_avg_sq[lo:hi].clone().cpu()})
-        return {"step": self._step, "per_param": per_param,
+            chunks.append({"numel": c.flat_param.numel(), "owned": tuple(c.owned), "master": c.master.clone().cpu(),
+                           "exp_avg": c.exp_avg.clone().cpu(), "exp_avg_sq": c.exp_avg_sq.clone().cpu()})
+        return {"step": self._step, "chunks": chunks,
                 "hyper": {k: v for k, v in self.param_groups[0].items() if k != "params"}}
 
     def load_state_dict(self, state):
         self._ensure_layout()
         self._step = state["step"]
-        it = iter(state["per_param"])
-        for c in self._chunks:
-            for lo, hi in c.spans:
-                rec = next(it)
-                c.master[lo:hi].copy_(rec["master"])
-                c.exp_avg[lo:hi].copy_(rec["exp_avg"])
-                c.exp_avg_sq[lo:hi].copy_(rec["exp_avg_sq"])
-            c.flat_param.copy_(c.master)
+        if len(state["chunks"]) != len(self._chunks):
+            raise ValueError(f"checkpoint has {len(state['chunks'])} optimizer buckets, this run has {len(self._chunks)} "
+                             "(different bucket size or model shard)")
+        for c, rec in zip(self._chunks, state["chunks"]):
+            if rec["numel"] != c.flat_param.numel() or tuple(rec["owned"]) != tuple(c.owned):
+                raise ValueError(f"optimizer state was saved for slice {tuple(rec['owned'])} of a {rec['numel']}-element "
+                                 f"bucket; this rank owns {tuple(c.owned)} of {c.flat_param.numel()} (the data-parallel "
+                                 "size or the bucket plan changed)")
+            c.master.copy_(rec["master"])
+            c.exp_avg.copy_(rec["exp_avg"])
+            c.exp_avg_sq.copy_(rec["exp_avg_sq"])
+            # the stored parameters are the rounding of the master weights where this rank has them;
+            # everywhere else they keep the values the model state dict restored
+            c.flat_param[c.owned[0] : c.owned[1]].copy_(c.master)
         for k, v in state.get("hyper", {}).items():
             self.param_groups[0][k] = v

@@ -278,12 +278,16 @@ def linear_cross_entropy(x, w_unembed, targets):
 # ------------------------------------------------------------------------------- MoE routing
 class _Router(torch.autograd.Function):
     """Fused fp32 router.  Outputs: gates [T,k] (grad -> x and w), ids [T,k], probs [T,E] and their
-    column means [E] (grad -> w only: the load-balancing loss sees detached tokens), counts [E]."""
+    column means [E], counts [E].  The gradient of the probabilities (the load-balancing loss) reaches
+    w only when `aux_to_tokens` is false - the loss then sees detached tokens, as in the reference's
+    CUDA backend (src/model/cuda_backend.py:39-41) - and also x when it is true, as in its torch
+    backend (src/model/torch_backend.py:153-155)."""
 
     @staticmethod
-    def forward(ctx, x, w, k):
+    def forward(ctx, x, w, k, aux_to_tokens=False):
         gates, idx, probs, counts, probs_mean = get_ext().router_topk(x.contiguous(), w.contiguous(), k)
         ctx.save_for_backward(x, w, gates, idx, probs)
+        ctx.aux_to_tokens = aux_to_tokens
         ctx.mark_non_differentiable(idx, counts)
         return gates, idx, probs, counts, probs_mean
 
@@ -294,14 +298,25 @@ class _Router(torch.autograd.Function):
         def f32(t):
             return None if t is None else t.float().contiguous()
 
-        # softmax / top-k / renormalise backward in one kernel; the two small products stay library GEMMs
+        # softmax / top-k / renormalise backward in one kernel, then two thin products on the tcgen05 GEMM
         dl_tok, dl_all = get_ext().router_bwd(gates, idx, probs, f32(dgates), f32(dprobs), f32(dprobs_mean), x)
+        dl_x = dl_all if ctx.aux_to_tokens else dl_tok
         dx = dw = None
+        thin = x.dim() == 2 and tc_ok(x, dl_x) and dl_x.shape[1] % 8 == 0
         if ctx.needs_input_grad[0]:
-            dx = dl_tok @ w.to(x.dtype)
+            w16 = w.to(x.dtype)
+            if thin and tc_ok(w16):
+                dx = torch.empty_like(x)
+                gemm_tc(dl_x, False, [w16], True, [dx])  # [T, E] x [E, d]
+            else:
+                dx = dl_x @ w16
         if ctx.needs_input_grad[1]:
-            dw = (dl_all.t() @ x).to(w.dtype)
-        return dx, dw, None
+            if thin and w.dtype == torch.float32:
+                dw = torch.empty_like(w)
+                wgrad(dl_all, x, [dw])  # dl_all^T x: reduction over the tokens, fp32 result
+            else:
+                dw = (dl_all.t() @ x).to(w.dtype)
+        return dx, dw, None, None
 
 
 def router_topk(x, w, k):
@@ -309,9 +324,9 @@ def router_topk(x, w, k):
     return _Router.apply(x, w, k)[:4]
 
 
-def router_topk_mean(x, w, k):
+def router_topk_mean(x, w, k, aux_to_tokens=False):
     """-> gates, ids, counts, mean router probability per expert [E] (what the load-balancing loss needs)."""
-    gates, idx, _probs, counts, probs_mean = _Router.apply(x, w, k)
+    gates, idx, _probs, counts, probs_mean = _Router.apply(x, w, k, aux_to_tokens)
     return gates, idx, counts, probs_mean
 
 

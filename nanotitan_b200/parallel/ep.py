@@ -50,7 +50,7 @@ def expert_parallel_moe(backend, flat: torch.Tensor, residual: torch.Tensor | No
     Returns (out [T, d], counts [E] of this rank's routing, mean router probabilities [E])."""
     cfg = backend.cfg
     with nvtx_range("moe/router"):
-        gates, top_e, counts, probs_mean = native.router_topk_mean(flat, backend.router.weight, cfg.top_k)
+        gates, top_e, counts, probs_mean = native.router_topk_mean(flat, backend.router.weight, cfg.top_k, backend.aux_to_tokens)
     with nvtx_range("moe/pack_tokens"):
         packed_x, packed_gate, packed_token, _, _, slot_of = native.pack(flat, gates, top_e, counts)
     if not hasattr(backend, "fused_exchange"):

@@ -27,6 +27,15 @@ MAX_RANKS = 16
 FLAG_WORDS = MAX_SLOTS * 2 * MAX_RANKS
 
 
+def owned_slice(numel: int, world: int, rank: int) -> tuple[int, int]:
+    """[lo, hi) of a `numel`-element bucket that rank `rank` of `world` reduces and updates: whole
+    16-byte vectors (8 16-bit elements), ceil-divided over the ranks - the split
+    `bucket_allreduce_kernel` computes on the device."""
+    per = ((numel // 8 + world - 1) // world) * 8
+    lo = min(numel, per * rank)
+    return lo, min(numel, lo + per)
+
+
 class BucketEngine:
     def __init__(self, group, device: torch.device):
         import torch.distributed._symmetric_memory as symm_mem
@@ -65,6 +74,9 @@ class BucketEngine:
         if not self.use_multicast:
             return 0
         return int(getattr(self._handles[t.data_ptr()], "multicast_ptr", 0) or 0)
+
+    def owned_slice(self, numel: int) -> tuple[int, int]:
+        return owned_slice(numel, self.world, self.rank)
 
     # ------------------------------------------------------------------ reducer interface
     def register(self, bucket) -> None:

@@ -15,7 +15,7 @@ import logging
 import torch
 
 from nanotitan_b200.data.dataset import PackedTokenDataset, SyntheticTokenDataset
-from nanotitan_b200.dist_env import cleanup, get_world_size, init_distributed, local_device
+from nanotitan_b200.dist_env import barrier, cleanup, get_world_size, init_distributed, local_device
 from nanotitan_b200.metrics import MetricsLogger, ScalarMetric, reduce_metrics
 from nanotitan_b200.models.model import NanoTitanModel
 from nanotitan_b200.models.utils import get_model_shard_specs
@@ -25,7 +25,7 @@ from nanotitan_b200.parallel_dims import get_parallel_dims
 from nanotitan_b200.profiler import build_profiler
 from nanotitan_b200.utils import load_run_config, reduce_scalars, seed_everything, setup_logging
 from nanotitan_b200.utils.checkpoint import latest_checkpoint, load_checkpoint, save_checkpoint
-from nanotitan_b200.utils.heartbeat import Heartbeat
+from nanotitan_b200.utils.heartbeat import Heartbeat, assert_peers_alive
 
 logger = logging.getLogger(__name__)
 
@@ -116,6 +116,16 @@ def main(argv=None) -> None:
             logger.info("resumed from %s at step %d", found, step)
 
     heartbeat = Heartbeat(cfg.fault.heartbeat_dir, dims.global_rank) if cfg.fault.heartbeat_dir else None
+    if heartbeat is not None:
+        heartbeat.beat(step)  # every rank is on record before anybody checks
+        barrier()
+
+    def check_peers() -> None:
+        """A peer whose heartbeat went stale is found here, on the host, before the next launch
+        (instead of after an in-kernel wait or a process-group timeout runs out)."""
+        if heartbeat is not None:
+            assert_peers_alive(cfg.fault.heartbeat_dir, world_size, cfg.fault.heartbeat_stale_s)
+
     profiler = build_profiler(cfg.run_name, cfg.profiler, dims)
     flops_per_token = model_flops_per_token(cfg, active_params)
     peak = cfg.hardware.peak_flops_tflops_per_gpu * 1e12
@@ -131,6 +141,7 @@ def main(argv=None) -> None:
                 progressed = False
                 for batch in train_loader:
                     progressed = True
+                    check_peers()
                     metrics = pp.train_step(model, batch, optimizer)
                     tokens_seen += tokens_per_step
                     metrics["train/tokens_per_step"] = ScalarMetric(tokens_per_step, reduce="none")
@@ -158,6 +169,7 @@ def main(argv=None) -> None:
                         heartbeat.beat(step)
                     every = cfg.checkpoint.every_steps
                     if cfg.checkpoint.dir and every and step % every == 0:
+                        check_peers()
                         save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg)
                     if step >= cfg.max_steps:
                         break
@@ -165,8 +177,11 @@ def main(argv=None) -> None:
                 if not progressed:
                     raise RuntimeError("the training loader produced no batch (dataset too small)")
         if cfg.checkpoint.dir:
+            check_peers()
             save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg)
     finally:
+        if heartbeat is not None:
+            heartbeat.leave(step)
         if metrics_logger is not None:
             metrics_logger.close()
         cleanup()

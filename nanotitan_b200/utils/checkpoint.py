@@ -50,6 +50,12 @@ def save_checkpoint(directory, step: int, tokens_seen: int, model, optimizer, di
     tmp = target.with_suffix(".tmp")
     torch.save(payload, tmp)
     os.replace(tmp, target)
+    # The manifest means "every shard is on disk": rank 0 writes it only after all ranks have
+    # renamed their file into place.
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
     if dims.global_rank == 0:
         manifest = {"step": step, "tokens_seen": tokens_seen, "world_size": dims.world_size,
                     "config": cfg.model_dump(mode="json") if cfg is not None and hasattr(cfg, "model_dump") else None}
@@ -59,15 +65,28 @@ def save_checkpoint(directory, step: int, tokens_seen: int, model, optimizer, di
     return step_dir
 
 
+def is_complete(step_dir) -> bool:
+    """A manifest plus one shard file per rank it names."""
+    step_dir = Path(step_dir)
+    manifest = step_dir / "manifest.json"
+    if not manifest.exists():
+        return False
+    try:
+        world = int(json.loads(manifest.read_text())["world_size"])
+    except (ValueError, KeyError, json.JSONDecodeError):
+        return False
+    return all(_rank_file(step_dir, r).exists() for r in range(world))
+
+
 def latest_checkpoint(directory) -> Path | None:
-    """Newest `step_*` folder that has a manifest (i.e. whose save completed on rank 0)."""
+    """Newest `step_*` folder whose save completed (manifest written and every rank's shard present)."""
     root = Path(directory)
-    if _STEP_DIR.search(root.name) and (root / "manifest.json").exists():
+    if _STEP_DIR.search(root.name) and is_complete(root):
         return root
     best = None
     for child in root.glob("step_*"):
         m = _STEP_DIR.search(child.name)
-        if m and (child / "manifest.json").exists():
+        if m and is_complete(child):
             if best is None or int(m.group(1)) > best[0]:
                 best = (int(m.group(1)), child)
     return None if best is None else best[1]
@@ -75,6 +94,17 @@ def latest_checkpoint(directory) -> Path | None:
 
 def load_checkpoint(step_dir, model, optimizer, dims) -> dict:
     payload = torch.load(_rank_file(Path(step_dir), dims.global_rank), map_location="cpu", weights_only=False)
+    saved = payload["coords"]
+    now = {"global_rank": dims.global_rank, "dp_rank": dims.dp_rank, "pp_rank": dims.pp_rank, "ep_rank": dims.ep_rank,
+           "dp_size": dims.dp_size, "pp_size": dims.pp_size, "ep_size": dims.ep_size}
+    if saved != now:
+        raise ValueError(f"checkpoint shard was written at {saved}, this rank is {now}: resume on the same "
+                         "dp x pp x ep layout, or rebuild the weights with `consolidate` + `load_full_state`")
+    spec_now = {"layer_start": model.spec.layer_start, "layer_end": model.spec.layer_end,
+                "start_expert_id": model.spec.start_expert_id, "end_expert_id": model.spec.end_expert_id,
+                "has_token_embed": model.spec.has_token_embed, "has_unembed_head": model.spec.has_unembed_head}
+    if payload["spec"] != spec_now:
+        raise ValueError(f"checkpoint shard covers {payload['spec']}, this rank's model shard is {spec_now}")
     with torch.no_grad():
         own = model.state_dict()
         for key, value in payload["model"].items():
@@ -90,6 +120,8 @@ def load_checkpoint(step_dir, model, optimizer, dims) -> dict:
 def consolidate(step_dir) -> dict[str, torch.Tensor]:
     """Merge the dp_rank-0 shards of every (pp, ep) coordinate into the state dict a
     single-process model (pp_size = ep_size = 1) would have."""
+    if not is_complete(step_dir):
+        raise FileNotFoundError(f"{step_dir} is not a complete checkpoint (manifest or rank shards missing)")
     shards = [torch.load(p, map_location="cpu", weights_only=False) for p in sorted(Path(step_dir).glob("rank_*.pt"))]
     shards = [s for s in shards if s["coords"]["dp_rank"] == 0]
     merged: dict[str, torch.Tensor] = {}

@@ -25,6 +25,11 @@ class Heartbeat:
         tmp.write_text(json.dumps({"rank": self.rank, "step": step, "time": time.time(), **extra}))
         os.replace(tmp, self.path)
 
+    def leave(self, step: int) -> None:
+        """Mark this rank as gone (clean exit or a caught failure): peers see it at their next check
+        without waiting for the file to age."""
+        self.beat(step, left=True)
+
     @staticmethod
     def read(directory: str | Path, rank: int) -> dict | None:
         path = Path(directory) / f"rank_{rank}.json"
@@ -39,7 +44,7 @@ class Heartbeat:
         stale = []
         for rank in range(world_size):
             rec = Heartbeat.read(directory, rank)
-            if rec is None or now - rec["time"] > max_age_s:
+            if rec is None or rec.get("left") or now - rec["time"] > max_age_s:
                 stale.append(rank)
         return stale
 
@@ -51,4 +56,4 @@ class RankFailure(RuntimeError):
 def assert_peers_alive(directory: str | Path, world_size: int, max_age_s: float) -> None:
     stale = Heartbeat.stale_ranks(directory, world_size, max_age_s)
     if stale:
-        raise RankFailure(f"ranks {stale} have no heartbeat newer than {max_age_s:.0f}s")
+        raise RankFailure(f"ranks {stale} have left or have no heartbeat newer than {max_age_s:.0f}s")

@@ -5,6 +5,7 @@ training resumes bit-exactly from a checkpoint."""
 import datetime
 import os
 import time
+from pathlib import Path
 
 import pytest
 import torch
@@ -51,6 +52,53 @@ def _lost_peer_worker(rank, world, hb_dir):
 @pytest.mark.distributed
 def test_survivor_detects_lost_peer_before_next_collective(tmp_path):
     run_distributed(_lost_peer_worker, 2, str(tmp_path))
+
+
+def _train_loop_worker(rank, world, tmp):
+    """The training loop itself: rank 1 is configured for one step and leaves cleanly after it, rank 0
+    for four.  Rank 0's loop must find rank 1 gone on the host, before it launches step 2."""
+    from nanotitan_b200 import train
+    from nanotitan_b200.parallel import PipelineParallel
+    from nanotitan_b200.sweep import dump_toml
+    from nanotitan_b200.utils.heartbeat import RankFailure
+    from tests.helpers import tiny_app_cfg
+
+    cfg = tiny_app_cfg(dp=2, batch=2).model_dump(mode="json")
+    cfg["max_steps"] = 4 if rank == 0 else 1
+    cfg["fault"] = {"pg_timeout_s": 30.0, "heartbeat_dir": str(Path(tmp) / "hb"), "heartbeat_stale_s": 60.0}
+    path = Path(tmp) / f"cfg{rank}.toml"
+    path.write_text(dump_toml(cfg), encoding="utf-8")
+    plain_step = PipelineParallel.train_step
+    steps_started = []
+
+    def counted_step(self, *a, **kw):
+        steps_started.append(1)
+        return plain_step(self, *a, **kw)
+
+    plain_check = train.assert_peers_alive
+
+    def late_check(*a, **kw):
+        if rank == 0 and steps_started:
+            time.sleep(1.5)  # the leaving rank has written its marker by the time this rank looks
+        return plain_check(*a, **kw)
+
+    PipelineParallel.train_step = counted_step
+    train.assert_peers_alive = late_check
+    try:
+        if rank == 0:
+            with pytest.raises(RankFailure):
+                train.main([str(path), "--synthetic-data", "--log.level", "WARNING"])
+            assert len(steps_started) == 1, "the stale peer must be found before step 2 is launched"
+        else:
+            train.main([str(path), "--synthetic-data", "--log.level", "WARNING"])
+    finally:
+        PipelineParallel.train_step = plain_step
+        train.assert_peers_alive = plain_check
+
+
+@pytest.mark.distributed
+def test_training_loop_stops_before_the_next_step_when_a_peer_left(tmp_path):
+    run_distributed(_train_loop_worker, 2, str(tmp_path))
 
 
 def _timeout_worker(rank, world, init_file):
