@@ -37,12 +37,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("scale"), py::arg("grads") = std::vector<at::Tensor>{}, "Causal flash attention backward -> (dq, dk, dv)");
   m.def("bucket_allreduce", &nt::bucket_allreduce, "Fused bucket all-reduce (+ AdamW) over peer / multicast memory");
   m.def("ep_allgather_counts", &nt::ep_allgather_counts, "All-gather per-expert counts through peer stores");
+  m.def("ep_dispatch", &nt::ep_dispatch, "Fused count exchange + pack + push of token rows into the expert ranks' staging buffers");
   m.def("ep_push_rows", &nt::ep_push_rows, "Push rows into peers' staging buffers (expert-parallel dispatch / return)");
   m.def("layer_norm_fwd", &nt::layer_norm_fwd);
   m.def("layer_norm_bwd", &nt::layer_norm_bwd, py::arg("dy"), py::arg("x"), py::arg("gamma"), py::arg("mean"), py::arg("rstd"),
         py::arg("dres") = py::none(), py::arg("dgamma_out") = py::none(), py::arg("dbeta_out") = py::none());
   m.def("cross_entropy_fwd_bwd", &nt::cross_entropy_fwd_bwd);
-  m.def("adamw_step", &nt::adamw_step);
+  m.def("adamw_step", &nt::adamw_step, py::arg("param"), py::arg("grad"), py::arg("master"), py::arg("m"), py::arg("v"), py::arg("step"),
+        py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("wd"), py::arg("grad_scale"), py::arg("want_sq"),
+        py::arg("bc_dev") = py::none());
   m.def("router_topk", &nt::router_topk);
   m.def("router_bwd", &nt::router_bwd);
   m.def("assign_slots", &nt::assign_slots);

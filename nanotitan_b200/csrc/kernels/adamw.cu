@@ -21,8 +21,12 @@ template <typename T, int VEC>
 __global__ void __launch_bounds__(AD_THREADS)
 adamw_kernel(T* __restrict__ param, const T* __restrict__ grad, float* __restrict__ master, float* __restrict__ m,
              float* __restrict__ v, long long n, float lr, float beta1, float beta2, float eps, float wd,
-             float bc1, float rsqrt_bc2, float grad_scale, float* __restrict__ sq_partial) {
+             float bc1, float rsqrt_bc2, float grad_scale, float* __restrict__ sq_partial, const float* __restrict__ bc_dev) {
   float local_sq = 0.f;
+  if (bc_dev != nullptr) {
+    bc1 = bc_dev[0];
+    rsqrt_bc2 = bc_dev[1];
+  }
   for (long long i = (static_cast<long long>(blockIdx.x) * AD_THREADS + threadIdx.x) * VEC; i < n;
        i += static_cast<long long>(gridDim.x) * AD_THREADS * VEC) {
     float g[VEC];
@@ -69,7 +73,8 @@ adamw_kernel(T* __restrict__ param, const T* __restrict__ grad, float* __restric
 
 // All buffers flat, same length (a multiple of 8), 16-byte aligned.  Returns sum(grad^2) partials or an empty tensor.
 at::Tensor adamw_step(at::Tensor param, const at::Tensor& grad, at::Tensor master, at::Tensor m, at::Tensor v, int64_t step,
-                      double lr, double beta1, double beta2, double eps, double wd, double grad_scale, bool want_sq) {
+                      double lr, double beta1, double beta2, double eps, double wd, double grad_scale, bool want_sq,
+                      const c10::optional<at::Tensor>& bc_dev) {
   TORCH_CHECK(param.is_cuda() && param.is_contiguous() && grad.is_contiguous() && master.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw_step: contiguous CUDA buffers");
   TORCH_CHECK(grad.scalar_type() == param.scalar_type() && master.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat, "adamw_step: dtypes");
   const long long n = param.numel();
@@ -83,13 +88,18 @@ at::Tensor adamw_step(at::Tensor param, const at::Tensor& grad, at::Tensor maste
   if (n == 0) return partial;
   const float bc1 = 1.f - static_cast<float>(std::pow(beta1, static_cast<double>(step)));
   const float bc2 = 1.f - static_cast<float>(std::pow(beta2, static_cast<double>(step)));
+  const float* bcp = nullptr;
+  if (bc_dev.has_value()) {
+    TORCH_CHECK(bc_dev->is_cuda() && bc_dev->scalar_type() == at::kFloat && bc_dev->numel() == 2, "adamw_step: bc_dev is two fp32 on the device");
+    bcp = bc_dev->data_ptr<float>();
+  }
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   NT_DISPATCH_FLOAT(param.scalar_type(), "adamw_step", [&] {
     constexpr int VEC = sizeof(scalar_t) == 4 ? 4 : 8;
     adamw_kernel<scalar_t, VEC><<<grid, AD_THREADS, 0, stream>>>(param.data_ptr<scalar_t>(), grad.data_ptr<scalar_t>(), master.data_ptr<float>(),
         m.data_ptr<float>(), v.data_ptr<float>(), n, static_cast<float>(lr), static_cast<float>(beta1), static_cast<float>(beta2),
         static_cast<float>(eps), static_cast<float>(wd), bc1, 1.f / std::sqrt(bc2), static_cast<float>(grad_scale),
-        want_sq ? partial.data_ptr<float>() : nullptr);
+        want_sq ? partial.data_ptr<float>() : nullptr, bcp);
   });
   NT_KERNEL_CHECK();
   return partial;

@@ -50,7 +50,8 @@ struct ArArgs {
   uint32_t* flag_peer[AR_MAX_RANKS];
   uint32_t* block_counter;  // local, one word per slot
   int rank, N, slot;
-  uint32_t epoch;
+  uint32_t* epoch_counter;  // local, one word per slot: epoch of the slot's previous launch
+  const float* bc_dev;      // optional {1 - beta1^t, 1 / sqrt(1 - beta2^t)} in device memory (CUDA-graph replays)
   long long n;  // elements, multiple of 8
   int fuse_adam, dtype;
   float lr, beta1, beta2, eps, wd, bc1, rsqrt_bc2;
@@ -115,15 +116,15 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8], int dtype) {
 
 // All ranks meet: raise my flag in every pad, wait for every flag in mine.  `phase` 0 = entry, 1 = exit.
 // Called by threads [0, N) of one block (`signal` = this block raises the flags).  Returns false on time-out.
-__device__ __forceinline__ bool cross_rank_barrier(const ArArgs& a, int phase, bool signal) {
+__device__ __forceinline__ bool cross_rank_barrier(const ArArgs& a, uint32_t epoch, int phase, bool signal) {
   const int t = threadIdx.x;
   bool ok = true;
   if (t < a.N) {
     const int word = (a.slot * 2 + phase) * AR_MAX_RANKS;
-    if (signal) st_release_sys(a.flag_peer[t] + word + a.rank, a.epoch);
+    if (signal) st_release_sys(a.flag_peer[t] + word + a.rank, epoch);
     const uint32_t* mine = a.flag_local + word + t;
     const long long start = clock64();
-    while (static_cast<int32_t>(ld_acquire_sys(mine) - a.epoch) < 0) {
+    while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
       if (clock64() - start > a.wait_cycles) {
         report_status(a.status, kStatusWaitTimeout, kKernelAllReduce, 1000u * static_cast<uint32_t>(phase) + static_cast<uint32_t>(t));
         ok = false;
@@ -139,11 +140,25 @@ __global__ void __launch_bounds__(AR_THREADS)
 bucket_allreduce_kernel(const ArArgs a) {
   __shared__ int s_ok;
   __shared__ unsigned s_last;
-  if (threadIdx.x == 0) s_ok = 1;
+  __shared__ float s_bc[2];
+  // The epoch is the slot's launch count: read here by every block, advanced by the last block to
+  // finish (after every block has read it), so the launch arguments are the same every step.
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_counter + a.slot) + 1u;
+  if (threadIdx.x == 0) {
+    s_ok = 1;
+    if (a.bc_dev != nullptr) {  // bias corrections that change per step without changing the launch
+      s_bc[0] = a.bc_dev[0];
+      s_bc[1] = a.bc_dev[1];
+    } else {
+      s_bc[0] = a.bc1;
+      s_bc[1] = a.rsqrt_bc2;
+    }
+  }
   __syncthreads();
+  const float bc1 = s_bc[0], rsqrt_bc2 = s_bc[1];
   // ---- 1. entry barrier (every block waits; block 0 raises the flags)
   if (blockIdx.x == 0 && threadIdx.x == 0) __threadfence_system();
-  if (!cross_rank_barrier(a, 0, blockIdx.x == 0)) s_ok = 0;
+  if (!cross_rank_barrier(a, epoch, 0, blockIdx.x == 0)) s_ok = 0;
   __syncthreads();
   const bool ok = s_ok != 0;
 
@@ -180,7 +195,7 @@ bucket_allreduce_kernel(const ArArgs a) {
           pw *= 1.f - a.lr * a.wd;
           mm = a.beta1 * mm + (1.f - a.beta1) * g[j];
           vv = a.beta2 * vv + (1.f - a.beta2) * g[j] * g[j];
-          pw -= (a.lr / a.bc1) * mm / (sqrtf(vv) * a.rsqrt_bc2 + a.eps);
+          pw -= (a.lr / bc1) * mm / (sqrtf(vv) * rsqrt_bc2 + a.eps);
           a.master[s] = pw; a.m[s] = mm; a.v[s] = vv;
           w[j] = pw;
         }
@@ -204,7 +219,9 @@ bucket_allreduce_kernel(const ArArgs a) {
   __syncthreads();
   if (s_last) {
     if (threadIdx.x == 0) a.block_counter[a.slot] = 0u;
-    if (ok) cross_rank_barrier(a, 1, true);
+    if (ok) cross_rank_barrier(a, epoch, 1, true);
+    __syncthreads();
+    if (threadIdx.x == 0) *reinterpret_cast<volatile uint32_t*>(a.epoch_counter + a.slot) = epoch;
   }
 }
 
@@ -214,7 +231,8 @@ bucket_allreduce_kernel(const ArArgs a) {
 void bucket_allreduce(at::Tensor grad_local, int64_t grad_mc, const at::Tensor& grad_peers, int64_t param_mc,
                       const at::Tensor& param_peers, const c10::optional<at::Tensor>& master, const c10::optional<at::Tensor>& m,
                       const c10::optional<at::Tensor>& v, at::Tensor flag_local, const at::Tensor& flag_peers, at::Tensor block_counter,
-                      int64_t rank, int64_t world, int64_t slot, int64_t epoch, int64_t step, double lr, double beta1, double beta2,
+                      int64_t rank, int64_t world, int64_t slot, at::Tensor epoch_counters, int64_t step,
+                      const c10::optional<at::Tensor>& bc_dev, double lr, double beta1, double beta2,
                       double eps, double wd, int64_t blocks, double wait_ms) {
   TORCH_CHECK(grad_local.is_cuda() && grad_local.is_contiguous(), "bucket_allreduce: contiguous CUDA bucket");
   TORCH_CHECK(grad_local.scalar_type() == at::kBFloat16 || grad_local.scalar_type() == at::kHalf, "bucket_allreduce: bf16 / fp16 buckets");
@@ -254,7 +272,12 @@ void bucket_allreduce(at::Tensor grad_local, int64_t grad_mc, const at::Tensor& 
   a.rank = static_cast<int>(rank);
   a.N = static_cast<int>(world);
   a.slot = static_cast<int>(slot);
-  a.epoch = static_cast<uint32_t>(epoch);
+  TORCH_CHECK(epoch_counters.is_cuda() && epoch_counters.scalar_type() == at::kInt && slot < epoch_counters.numel(), "bucket_allreduce: epoch counters");
+  a.epoch_counter = reinterpret_cast<uint32_t*>(epoch_counters.data_ptr());
+  if (bc_dev.has_value()) {
+    TORCH_CHECK(bc_dev->is_cuda() && bc_dev->scalar_type() == at::kFloat && bc_dev->numel() == 2, "bucket_allreduce: bc_dev is two fp32 on the device");
+    a.bc_dev = bc_dev->data_ptr<float>();
+  }
   a.n = grad_local.numel();
   a.dtype = grad_local.scalar_type() == at::kBFloat16 ? 1 : 0;
   a.lr = static_cast<float>(lr); a.beta1 = static_cast<float>(beta1); a.beta2 = static_cast<float>(beta2);

@@ -56,8 +56,11 @@ std::vector<at::Tensor> layer_norm_bwd(const at::Tensor& dy, const at::Tensor& x
                                        const c10::optional<at::Tensor>& dgamma_out,
                                        const c10::optional<at::Tensor>& dbeta_out);
 at::Tensor cross_entropy_fwd_bwd(at::Tensor logits, const at::Tensor& targets, int64_t V, double grad_scale, bool write_grad);
+// `bc_dev` (optional, fp32 [2] on the device): {1 - beta1^t, 1 / sqrt(1 - beta2^t)} read by the kernel instead of being
+// computed from `step` on the host, so that a captured launch stays valid as t advances.
 at::Tensor adamw_step(at::Tensor param, const at::Tensor& grad, at::Tensor master, at::Tensor m, at::Tensor v, int64_t step,
-                      double lr, double beta1, double beta2, double eps, double wd, double grad_scale, bool want_sq);
+                      double lr, double beta1, double beta2, double eps, double wd, double grad_scale, bool want_sq,
+                      const c10::optional<at::Tensor>& bc_dev);
 
 // ---- flash attention (flash_attn.cu): [B, S, H, Dh] tensors, Dh in {32, 64}
 std::vector<at::Tensor> flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale);
@@ -68,15 +71,21 @@ std::vector<at::Tensor> flash_bwd(const at::Tensor& dout, const at::Tensor& q, c
 void bucket_allreduce(at::Tensor grad_local, int64_t grad_mc, const at::Tensor& grad_peers, int64_t param_mc,
                       const at::Tensor& param_peers, const c10::optional<at::Tensor>& master, const c10::optional<at::Tensor>& m,
                       const c10::optional<at::Tensor>& v, at::Tensor flag_local, const at::Tensor& flag_peers, at::Tensor block_counter,
-                      int64_t rank, int64_t world, int64_t slot, int64_t epoch, int64_t step, double lr, double beta1, double beta2,
+                      int64_t rank, int64_t world, int64_t slot, at::Tensor epoch_counters, int64_t step,
+                      const c10::optional<at::Tensor>& bc_dev, double lr, double beta1, double beta2,
                       double eps, double wd, int64_t blocks, double wait_ms);
 
 // ---- expert-parallel row exchange over NVLink peer memory (ep_exchange.cu)
 void ep_allgather_counts(const at::Tensor& counts, const at::Tensor& cmat_peers, at::Tensor flag_local, const at::Tensor& flag_peers,
-                         int64_t rank, int64_t world, int64_t epoch, int64_t word_base, double wait_ms);
+                         int64_t rank, int64_t world, at::Tensor epoch_counter, int64_t word_base, double wait_ms);
+std::vector<at::Tensor> ep_dispatch(const at::Tensor& x, const at::Tensor& gates, const at::Tensor& idx, const at::Tensor& slot_of,
+                                    const at::Tensor& counts, const at::Tensor& offsets, at::Tensor cmat_local,
+                                    const at::Tensor& cmat_peers, const at::Tensor& dst_peers, int64_t capacity_rows, int64_t E_loc,
+                                    at::Tensor block_counter, at::Tensor flag_local, const at::Tensor& flag_peers, int64_t rank,
+                                    int64_t world, at::Tensor epoch_counter, double wait_ms, int64_t blocks);
 void ep_push_rows(const at::Tensor& src, const at::Tensor& dst_peers, int64_t dst_capacity_rows, const at::Tensor& cmat, int64_t E_loc,
-                  int64_t direction, at::Tensor block_counter, at::Tensor flag_local, const at::Tensor& flag_peers, int64_t rank,
-                  int64_t world, int64_t epoch, int64_t word_base, double wait_ms, int64_t blocks);
+                  int64_t direction, bool entry_barrier, at::Tensor block_counter, at::Tensor flag_local, const at::Tensor& flag_peers,
+                  int64_t rank, int64_t world, at::Tensor epoch_counter, int64_t word_base, double wait_ms, int64_t blocks);
 
 // ---- MoE routing / dispatch
 std::vector<at::Tensor> router_topk(const at::Tensor& x, const at::Tensor& w, int64_t k);

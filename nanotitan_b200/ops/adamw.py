@@ -54,6 +54,10 @@ class FusedAdamW(torch.optim.Optimizer):
         self._step = 0
         self.track_grad_norm = track_grad_norm
         self._sq_parts: list[torch.Tensor] = []
+        # Bias corrections of the step in flight, in device memory, for launches that are captured in a
+        # CUDA graph (their arguments cannot change from step to step); None = computed per launch.
+        self._bc_dev: torch.Tensor | None = None
+        self._bc_host: torch.Tensor | None = None
 
     # ------------------------------------------------------------------ layout
     def bind_reducers(self, reducers: dict) -> None:
@@ -75,6 +79,24 @@ class FusedAdamW(torch.optim.Optimizer):
             self._own_reducer = ReducerV1(rest, 1, None, bucket_size=1 << 20)
             for b in self._own_reducer.buckets:
                 self._chunks.append(_Chunk(b, b.params, b.spans))
+
+    def enable_device_constants(self, device) -> None:
+        """Keep the per-step bias corrections in device memory (see `stage_step_constants`)."""
+        if self._bc_dev is None:
+            self._bc_dev = torch.zeros(2, dtype=torch.float32, device=device)
+            self._bc_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+
+    def stage_step_constants(self) -> None:
+        """Copy the bias corrections of the next step to the device (one 8-byte stream-ordered copy);
+        call before every step whose kernels were captured with `device_constants()`."""
+        beta1, beta2 = self.param_groups[0]["betas"]
+        t = self._step + 1
+        self._bc_host[0] = 1.0 - beta1 ** t
+        self._bc_host[1] = 1.0 / (1.0 - beta2 ** t) ** 0.5
+        self._bc_dev.copy_(self._bc_host, non_blocking=True)
+
+    def device_constants(self):
+        return self._bc_dev
 
     def next_step(self) -> int:
         """Step number the update in flight belongs to (bucket kernels run before `step()`)."""
@@ -114,7 +136,7 @@ class FusedAdamW(torch.optim.Optimizer):
             if grads.is_cuda:
                 part = get_ext().adamw_step(c.flat_param, grads, c.master, c.exp_avg, c.exp_avg_sq, self._step,
                                             group["lr"], beta1, beta2, group["eps"], group["weight_decay"], 1.0,
-                                            self.track_grad_norm)
+                                            self.track_grad_norm, self._bc_dev)
                 if self.track_grad_norm:
                     self._sq_parts.append(part.sum())
             else:

@@ -9,9 +9,11 @@ Two transports move the rows:
   * `exchange = "nccl"`: count exchange + `all_to_all_single` with host-side split sizes +
     a regroup gather (the data flow of the reference's torch backend,
     src/model/torch_backend.py:72-147, with every other step on the native kernels).
-  * `exchange = "p2p"`: `nanotitan_b200.parallel.ep_fused` pushes rows straight into the
-    destination's expert-major buffer over NVLink from inside a kernel (no host sync, no
-    regroup pass); used when the symmetric buffers could be set up.
+  * `exchange = "p2p"` (the default on GPUs): `nanotitan_b200.parallel.ep_fused` - one kernel
+    exchanges the counts and stores every token row straight into its expert rank's expert-major
+    staging buffer over NVLink, the grouped GEMMs read that buffer in place, one kernel stores
+    the expert outputs into the home rank's packed-order buffer and the combine gathers from it
+    (no host sync, no packed copy, no regroup pass).
 """
 from __future__ import annotations
 
@@ -51,23 +53,28 @@ def expert_parallel_moe(backend, flat: torch.Tensor, residual: torch.Tensor | No
     cfg = backend.cfg
     with nvtx_range("moe/router"):
         gates, top_e, counts, probs_mean = native.router_topk_mean(flat, backend.router.weight, cfg.top_k, backend.aux_to_tokens)
-    with nvtx_range("moe/pack_tokens"):
-        packed_x, packed_gate, packed_token, _, _, slot_of = native.pack(flat, gates, top_e, counts)
     if not hasattr(backend, "fused_exchange"):
         from nanotitan_b200.parallel import ep_fused
 
         ok = flat.dtype in (torch.bfloat16, torch.float16) and flat.shape[1] % 8 == 0
         backend.fused_exchange = ep_fused.get_exchange(backend.spec.ep_group, cfg.num_experts, flat.device) if ok else None
     fused = backend.fused_exchange
-    with nvtx_range("moe/dispatch"):
-        if fused is not None:
-            expert_in, local_offsets, ctx = fused.dispatch(packed_x, counts)
-        else:
+    if fused is not None:
+        with nvtx_range("moe/dispatch"):
+            expert_in, local_offsets, packed_gate, packed_token, slot_of, ctx = fused.dispatch(flat, gates, top_e, counts)
+        with nvtx_range("moe/expert_compute"):
+            expert_out = backend.experts(expert_in, local_offsets)
+        with nvtx_range("moe/return"):
+            returned = fused.gather_back(expert_out, ctx)
+    else:
+        with nvtx_range("moe/pack_tokens"):
+            packed_x, packed_gate, packed_token, _, _, slot_of = native.pack(flat, gates, top_e, counts)
+        with nvtx_range("moe/dispatch"):
             expert_in, local_offsets, ctx = _nccl_exchange(backend, packed_x, counts)
-    with nvtx_range("moe/expert_compute"):
-        expert_out = backend.experts(expert_in, local_offsets)
-    with nvtx_range("moe/return"):
-        returned = fused.gather_back(expert_out, ctx) if fused is not None else _nccl_return(expert_out, ctx)
+        with nvtx_range("moe/expert_compute"):
+            expert_out = backend.experts(expert_in, local_offsets)
+        with nvtx_range("moe/return"):
+            returned = _nccl_return(expert_out, ctx)
     with nvtx_range("moe/combine_tokens"):
         out = native.combine(returned, packed_gate, packed_token, slot_of, flat.shape[0], residual)
     return out, counts, probs_mean

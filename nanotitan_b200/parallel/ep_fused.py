@@ -1,22 +1,39 @@
 """Expert-parallel dispatch / return with kernels that write straight into peer memory.
 
-`FusedExchange` holds, for one expert-parallel group, symmetric staging buffers (mapped into
-every peer), the all-gathered count matrix and a flag pad.  A layer's forward does:
+`FusedExchange` holds, for one expert-parallel group, symmetric buffers (mapped into every peer),
+the count matrix and a flag pad.  One layer's forward is
 
-    counts --ep_allgather_counts--> C[src][expert]           (peer stores + flag barrier)
-    packed rows --ep_push_rows(0)--> expert ranks' staging    (already expert-major there)
-    ... grouped expert GEMMs ...
-    expert outputs --ep_push_rows(1)--> home ranks' staging   (already in packed order there)
+    x, routing --ep_dispatch--> expert ranks' staging X_in     (count exchange + pack + push, one kernel)
+    ... grouped expert GEMMs read X_in in place ...
+    expert outputs --ep_push_rows(1)--> home ranks' staging Y  (already in packed order there)
+    ... combine gathers from Y in place ...
 
-and backward runs the two pushes the other way round.  Compared with the NCCL path
-(`parallel/ep.py::_nccl_exchange`) there is no count collective, no split-size read-back for the
-collective, no send/receive buffers and no regrouping gather/scatter.  One 4-byte host read per
-layer remains: the number of rows this rank received, needed to size the activation tensors.
+and backward runs two pushes the other way round (combine-backward rows to the expert ranks,
+dispatch-backward rows home).  Compared with the NCCL path (`parallel/ep.py::_nccl_exchange`) there
+is no count collective, no split-size read-back, no packed copy on the home rank, no send / receive
+buffers and no regrouping gather / scatter; the host never waits inside a step.
+
+Memory.  X_in and Y of a layer stay alive until that layer's backward (they are what the weight
+gradient and the combine backward read), so they come from a pool of symmetric buffers: `acquire`
+hands out a free buffer (allocating - a collective over the group - when none fits), `release`
+returns it when the layer's backward has used it, `reset` returns everything at the start of a
+step.  Every rank runs the same layers in the same order, so the pools evolve identically and a
+buffer is the same symmetric allocation on every rank.  Expert-side buffers hold
+`capacity_factor x` this rank's own assignment count (at most ep x, the true worst case); rows
+beyond that are dropped by the kernel, which records it in the device status word, and the step
+then fails with a message naming `NT_EP_CAPACITY_FACTOR`.
+
+Ordering.  Only the dispatch kernel opens with a cross-rank barrier (it carries the counts).  The
+other three transfers start without one: each writes a buffer whose last readers on the peers were
+enqueued before a kernel that ended with a cross-rank barrier this rank has already passed (the
+dispatch of the same layer, or the previous transfer of the same backward), so those reads are over.
+All transfers end with a barrier: every rank's rows have landed when the kernel completes.
+
 Symmetric memory and its rendezvous come from `torch.distributed._symmetric_memory`.
 """
 from __future__ import annotations
 
-import logging
+import math
 import os
 
 import torch
@@ -24,9 +41,19 @@ import torch.distributed as dist
 
 from nanotitan_b200.ops.ext import get_ext
 
-logger = logging.getLogger(__name__)
-
 FLAG_WORDS = 64
+
+
+class _SymmBuffer:
+    """One symmetric allocation viewed as [rows, d], with every rank's address of it."""
+
+    __slots__ = ("flat", "peers", "numel", "dtype")
+
+    def __init__(self, flat, peers):
+        self.flat, self.peers, self.numel, self.dtype = flat, peers, flat.numel(), flat.dtype
+
+    def view(self, rows: int, d: int) -> torch.Tensor:
+        return self.flat[: rows * d].view(rows, d)
 
 
 class FusedExchange:
@@ -39,11 +66,8 @@ class FusedExchange:
         self.E = num_experts
         self.E_loc = num_experts // self.ep
         self.wait_ms = float(os.environ.get("NT_COMM_WAIT_MS", "60000"))
-        self.blocks = int(os.environ.get("NT_EP_BLOCKS", "96"))
-        # NT_EP_HOST_COUNTS=1: read the received row count back per layer (exact-size buffers, one
-        # host sync per layer).  Default: size the expert-side buffers for the worst case and keep
-        # the count on the device, so the host never waits inside a step.
-        self.host_counts = os.environ.get("NT_EP_HOST_COUNTS", "0") == "1"
+        self.blocks = int(os.environ.get("NT_EP_BLOCKS", "128"))
+        self.capacity_factor = float(os.environ.get("NT_EP_CAPACITY_FACTOR", "2.0"))
         self._handles = {}
         self.flags = self._alloc(FLAG_WORDS, torch.int32)
         self.flags.zero_()
@@ -52,12 +76,15 @@ class FusedExchange:
         self.cmat.zero_()
         self.cmat_peers = self._peers(self.cmat)
         self.block_counter = torch.zeros(1, dtype=torch.int32, device=device)
-        self.epoch = 0
-        self.staging: dict[int, torch.Tensor] = {}       # direction -> [capacity, d]
-        self.staging_peers: dict[int, torch.Tensor] = {}
+        self.epoch_counter = torch.zeros(1, dtype=torch.int32, device=device)  # advanced by the kernels themselves
+        self._free: list[_SymmBuffer] = []
+        self._used: list[_SymmBuffer] = []
+        self._fixed: dict[str, _SymmBuffer] = {}
+        self.allocated_bytes = 0
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
+    # ------------------------------------------------------------------ symmetric memory
     def _alloc(self, numel, dtype):
         t = self.symm_mem.empty(numel, dtype=dtype, device=self.device)
         self._handles[t.data_ptr()] = self.symm_mem.rendezvous(t, self.group)
@@ -66,100 +93,163 @@ class FusedExchange:
     def _peers(self, t):
         return torch.tensor(list(self._handles[t.data_ptr()].buffer_ptrs), dtype=torch.int64)
 
-    def _staging_for(self, direction: int, rows: int, d: int, dtype) -> torch.Tensor:
-        """Staging buffer rows land in: direction 0 -> expert side (worst case ep * A rows),
-        direction 1 -> home side (A rows).  Every rank sees the same shapes, so (re)allocation
-        happens on all ranks at the same call."""
-        buf = self.staging.get(direction)
-        if buf is None or buf.shape[0] < rows or buf.shape[1] != d or buf.dtype != dtype:
-            flat = self._alloc(rows * d, dtype)
-            buf = flat.view(rows, d)
-            self.staging[direction] = buf
-            self.staging_peers[direction] = self._peers(flat)
+    def _new_buffer(self, numel: int, dtype) -> _SymmBuffer:
+        flat = self._alloc(numel, dtype)
+        self.allocated_bytes += numel * flat.element_size()
+        return _SymmBuffer(flat, self._peers(flat))
+
+    def acquire(self, rows: int, d: int, dtype) -> _SymmBuffer:
+        """A free pooled buffer of at least rows x d elements (first fit in pool order, else a new
+        allocation, which every rank makes at the same call)."""
+        need = rows * d
+        for i, buf in enumerate(self._free):
+            if buf.numel >= need and buf.dtype == dtype:
+                self._used.append(self._free.pop(i))
+                return buf
+        buf = self._new_buffer(need, dtype)
+        self._used.append(buf)
         return buf
 
-    def _next_epoch(self) -> int:
-        self.epoch += 1
-        return self.epoch
+    def release(self, buf: _SymmBuffer) -> None:
+        for i, other in enumerate(self._used):
+            if other is buf:
+                self._free.append(self._used.pop(i))
+                return
+
+    def reset(self) -> None:
+        """Start of a step: buffers whose layer never ran backward go back to the pool."""
+        self._free.extend(self._used)
+        self._used = []
+
+    def fixed(self, name: str, rows: int, d: int, dtype) -> _SymmBuffer:
+        """A named buffer that is reused by every layer (the two backward transfers)."""
+        buf = self._fixed.get(name)
+        if buf is None or buf.numel < rows * d or buf.dtype != dtype:
+            buf = self._new_buffer(rows * d, dtype)
+            self._fixed[name] = buf
+        return buf
+
+    def capacity_rows(self, assignments: int) -> int:
+        """Rows an expert rank's buffers hold for a layer in which every rank routes `assignments` rows."""
+        bounded = int(math.ceil(self.capacity_factor * assignments / 128.0)) * 128
+        return max(128, min(self.ep * assignments, bounded))
 
     # ------------------------------------------------------------------ primitives
     def allgather_counts(self, counts: torch.Tensor) -> torch.Tensor:
         get_ext().ep_allgather_counts(counts.to(torch.int32).contiguous(), self.cmat_peers, self.flags, self.flag_peers,
-                                      self.rank, self.ep, self._next_epoch(), 0, self.wait_ms)
+                                      self.rank, self.ep, self.epoch_counter, 0, self.wait_ms)
         return self.cmat.clone()
 
-    def push(self, rows: torch.Tensor, cmat: torch.Tensor, direction: int, assignments: int, out_rows: int,
-             landed: torch.Tensor | None = None) -> torch.Tensor:
-        """`landed` (int32 [1] on the device): how many rows arrive here, when `out_rows` is only the
-        worst case; the rows past it in the result are uninitialised and nobody reads them."""
-        cap = self.ep * assignments if direction == 0 else assignments
-        staging = self._staging_for(direction, cap, rows.shape[1], rows.dtype)
-        get_ext().ep_push_rows(rows.contiguous(), self.staging_peers[direction], staging.shape[0], cmat, self.E_loc, direction,
-                               self.block_counter, self.flags, self.flag_peers, self.rank, self.ep, self._next_epoch(), 0,
+    def push(self, rows: torch.Tensor, cmat: torch.Tensor, direction: int, dst: _SymmBuffer, dst_rows: int,
+             entry_barrier: bool = False) -> torch.Tensor:
+        """Move `rows` into the peers' `dst` buffers (layout change of `direction`); returns this
+        rank's view [dst_rows, d] of `dst`, complete when the kernel has finished."""
+        get_ext().ep_push_rows(rows.contiguous(), dst.peers, dst_rows, cmat, self.E_loc, direction, entry_barrier,
+                               self.block_counter, self.flags, self.flag_peers, self.rank, self.ep, self.epoch_counter, 0,
                                self.wait_ms, self.blocks)
-        if landed is None:
-            return staging[:out_rows].clone()
-        out = torch.empty(out_rows, rows.shape[1], dtype=rows.dtype, device=rows.device)
-        get_ext().copy_rows_prefix(staging, out, landed)
-        return out
+        return dst.view(dst_rows, rows.shape[1])
 
     # ------------------------------------------------------------------ layer interface (see parallel/ep.py)
-    def dispatch(self, packed_x: torch.Tensor, counts: torch.Tensor):
-        cmat = self.allgather_counts(counts)
-        mine = cmat[:, self.rank * self.E_loc : (self.rank + 1) * self.E_loc]
-        per_expert = mine.sum(dim=0)
-        local_offsets = torch.zeros(self.E_loc + 1, dtype=torch.int32, device=packed_x.device)
-        local_offsets[1:] = torch.cumsum(per_expert, dim=0)
-        assignments = packed_x.shape[0]
-        if self.host_counts:
-            received = int(local_offsets[-1].item())  # the layer's one host read
-            if not 0 <= received <= self.ep * assignments:
-                raise RuntimeError(
-                    f"expert-parallel count exchange returned {received} rows for rank {self.rank}; at most "
-                    f"{self.ep * assignments} can arrive (count matrix: {cmat.tolist()})"
-                )
-            landed = None
-        else:
-            # Worst case: every rank sends all its assignments here.  The grouped GEMMs walk the
-            # tiles that `local_offsets` describes, so the unused tail costs memory, not time.
-            received = self.ep * assignments
-            landed = local_offsets[-1:]
-        expert_in = _Push.apply(packed_x, self, cmat, 0, assignments, received, landed, None)
-        return expert_in, local_offsets, (cmat, assignments, landed)
+    def dispatch(self, x: torch.Tensor, gates: torch.Tensor, idx: torch.Tensor, counts: torch.Tensor):
+        """-> (expert_in [capacity, d] view of this rank's staging, local_offsets [E_loc + 1],
+        packed_gate [A], packed_token [A], slot_of [T, k], context for `gather_back`)."""
+        return _Dispatch.apply(x, gates, self, idx, counts)
 
     def gather_back(self, expert_out: torch.Tensor, ctx) -> torch.Tensor:
-        cmat, assignments, landed = ctx
-        return _Push.apply(expert_out, self, cmat, 1, assignments, assignments, None, landed)
+        return _Return.apply(expert_out, self, ctx)
 
 
-class _Push(torch.autograd.Function):
+class _LayerContext:
+    """What the transfers of one layer share: its count matrix and buffers."""
+
+    __slots__ = ("cmat", "assignments", "capacity", "x_in", "y_home", "d", "dtype")
+
+
+class _Dispatch(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, rows, exchange, cmat, direction, assignments, out_rows, landed, landed_back):
-        """`landed` / `landed_back`: device-side row counts of the result / of the gradient that
-        travels the other way, when their host-side sizes are worst-case bounds (else None)."""
-        ctx.exchange, ctx.cmat, ctx.direction, ctx.assignments, ctx.in_rows = exchange, cmat, direction, assignments, rows.shape[0]
-        ctx.landed_back = landed_back
-        return exchange.push(rows, cmat, direction, assignments, out_rows, landed)
+    def forward(ctx, x, gates, exchange, idx, counts):
+        ext = get_ext()
+        offsets, slot_of = ext.assign_slots(idx, counts)
+        tokens, d = x.shape
+        layer = _LayerContext()
+        layer.assignments = tokens * idx.shape[1]
+        layer.capacity = exchange.capacity_rows(layer.assignments)
+        layer.d, layer.dtype = d, x.dtype
+        # both forward buffers are taken before the dispatch kernel is enqueued: its barriers then
+        # order every peer's earlier reads of them before the first store into them
+        layer.x_in = exchange.acquire(layer.capacity, d, x.dtype)
+        layer.y_home = exchange.acquire(layer.assignments, d, x.dtype)
+        cmat, local_offsets, packed_token, packed_gate = ext.ep_dispatch(
+            x.contiguous(), gates.contiguous(), idx, slot_of, counts, offsets, exchange.cmat, exchange.cmat_peers,
+            layer.x_in.peers, layer.capacity, exchange.E_loc, exchange.block_counter, exchange.flags, exchange.flag_peers,
+            exchange.rank, exchange.ep, exchange.epoch_counter, exchange.wait_ms, exchange.blocks)
+        layer.cmat = cmat
+        ctx.exchange, ctx.layer, ctx.tokens = exchange, layer, tokens
+        ctx.save_for_backward(slot_of)
+        expert_in = layer.x_in.view(layer.capacity, d)
+        ctx.mark_non_differentiable(local_offsets, packed_token, slot_of)
+        ctx.set_materialize_grads(False)
+        return expert_in, local_offsets, packed_gate, packed_token, slot_of, _Opaque(layer)
 
     @staticmethod
-    def backward(ctx, grad):
-        back = ctx.exchange.push(grad, ctx.cmat, 1 - ctx.direction, ctx.assignments, ctx.in_rows, ctx.landed_back)
-        return back, None, None, None, None, None, None, None
+    def backward(ctx, d_expert_in, _doff, d_packed_gate, _dtok, _dslot, _dctx):
+        (slot_of,) = ctx.saved_tensors
+        exchange, layer = ctx.exchange, ctx.layer
+        dx = None
+        if d_expert_in is not None:
+            home = exchange.fixed("dx_home", layer.assignments, layer.d, layer.dtype)
+            landed = exchange.push(d_expert_in, layer.cmat, 1, home, layer.assignments)
+            dx = get_ext().pack_bwd(landed, slot_of.view(-1), None, ctx.tokens)
+        dgates = d_packed_gate[slot_of.long()] if d_packed_gate is not None else None
+        exchange.release(layer.x_in)  # the weight-gradient GEMMs that read it are already enqueued
+        return dx, dgates, None, None, None
+
+
+class _Opaque:
+    """Carries a Python object through an autograd Function's outputs."""
+
+    def __init__(self, value):
+        self.value = value
+
+
+class _Return(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, expert_out, exchange, opaque):
+        layer = opaque.value
+        ctx.exchange, ctx.layer = exchange, layer
+        return exchange.push(expert_out, layer.cmat, 1, layer.y_home, layer.assignments)
+
+    @staticmethod
+    def backward(ctx, d_returned):
+        exchange, layer = ctx.exchange, ctx.layer
+        dst = exchange.fixed("dy_expert", layer.capacity, layer.d, layer.dtype)
+        d_expert_out = exchange.push(d_returned, layer.cmat, 0, dst, layer.capacity)
+        exchange.release(layer.y_home)  # combine-backward, its last reader, ran before this node
+        return d_expert_out, None, None
 
 
 _EXCHANGES: dict = {}
 
 
 def get_exchange(group, num_experts: int, device: torch.device):
-    """One `FusedExchange` per expert-parallel group (shared by all layers); None when disabled or
-    when symmetric memory cannot be set up (the NCCL path is used then)."""
+    """One `FusedExchange` per expert-parallel group (shared by all layers).  None only when the
+    fused path is switched off (`NT_FUSED_EP=0`); a set-up failure raises instead of silently
+    falling back to the NCCL path."""
     if os.environ.get("NT_FUSED_EP", "1") == "0" or group is None:
         return None
     key = id(group)
     if key not in _EXCHANGES:
         try:
             _EXCHANGES[key] = FusedExchange(group, num_experts, device)
-        except Exception as exc:  # noqa: BLE001
-            logger.warning("fused expert-parallel exchange unavailable (%s: %s); using NCCL", type(exc).__name__, exc)
-            _EXCHANGES[key] = None
+        except Exception as exc:
+            raise RuntimeError(
+                f"the fused expert-parallel exchange could not be set up ({type(exc).__name__}: {exc}); "
+                "set NT_FUSED_EP=0 to run the NCCL all-to-all path on purpose") from exc
     return _EXCHANGES[key]
+
+
+def reset_pools() -> None:
+    """Return every pooled buffer (called at the start of a training step)."""
+    for exchange in _EXCHANGES.values():
+        if exchange is not None:
+            exchange.reset()

@@ -54,7 +54,8 @@ class BucketEngine:
         self.flags.zero_()
         self.flag_peers = self._peer_table(self.flags)
         self.block_counter = torch.zeros(MAX_SLOTS, dtype=torch.int32, device=device)
-        self.epoch: dict[int, int] = {}
+        # per-slot launch counts, advanced by the kernel itself: a launch has the same arguments every step
+        self.epoch_counters = torch.zeros(MAX_SLOTS, dtype=torch.int32, device=device)
         self.slots: dict[int, int] = {}
         self.optim: dict[int, tuple] = {}
         torch.cuda.synchronize(device)
@@ -84,7 +85,6 @@ class BucketEngine:
         if key not in self.slots:
             self.slots[key] = len(self.slots)
             assert self.slots[key] < MAX_SLOTS, "too many buckets for the flag pad"
-            self.epoch[key] = 0
             bucket._peers = self._peer_table(bucket.buffer)
             bucket._mc = self._multicast(bucket.buffer)
 
@@ -98,7 +98,6 @@ class BucketEngine:
 
         self.register(bucket)
         key = id(bucket)
-        self.epoch[key] += 1
         ready = torch.cuda.Event()
         ready.record()
         self.stream.wait_event(ready)
@@ -109,14 +108,14 @@ class BucketEngine:
                 hyper = opt.param_groups[0]
                 get_ext().bucket_allreduce(
                     bucket.buffer, bucket._mc, bucket._peers, param_mc, param_peers, master, m, v, self.flags,
-                    self.flag_peers, self.block_counter, self.rank, self.world, self.slots[key], self.epoch[key],
-                    opt.next_step(), hyper["lr"], hyper["betas"][0], hyper["betas"][1], hyper["eps"],
+                    self.flag_peers, self.block_counter, self.rank, self.world, self.slots[key], self.epoch_counters,
+                    opt.next_step(), opt.device_constants(), hyper["lr"], hyper["betas"][0], hyper["betas"][1], hyper["eps"],
                     hyper["weight_decay"], self.blocks, self.wait_ms)
             else:
                 get_ext().bucket_allreduce(
                     bucket.buffer, bucket._mc, bucket._peers, 0, bucket._peers, None, None, None, self.flags,
-                    self.flag_peers, self.block_counter, self.rank, self.world, self.slots[key], self.epoch[key],
-                    1, 0.0, 0.9, 0.999, 1e-8, 0.0, self.blocks, self.wait_ms)
+                    self.flag_peers, self.block_counter, self.rank, self.world, self.slots[key], self.epoch_counters,
+                    1, None, 0.0, 0.9, 0.999, 1e-8, 0.0, self.blocks, self.wait_ms)
             done = torch.cuda.Event()
             done.record()
         return done
@@ -136,13 +135,15 @@ def attach_if_possible(reducer) -> bool:
 
 
 def make_engine(group, group_size: int, device: torch.device):
-    """-> BucketEngine or None (single rank, disabled, or symmetric memory unavailable)."""
+    """-> BucketEngine, or None for a single rank or when switched off (`NT_FUSED_ALLREDUCE=0`).
+    A set-up failure raises: the NCCL path is never taken silently."""
     if group is None or group_size < 2 or device.type != "cuda" or group_size > MAX_RANKS:
         return None
     if os.environ.get("NT_FUSED_ALLREDUCE", "1") == "0":
         return None
     try:
         return BucketEngine(group, device)
-    except Exception as exc:  # noqa: BLE001 - any failure here means "use NCCL"
-        logger.warning("fused all-reduce unavailable (%s: %s); using NCCL", type(exc).__name__, exc)
-        return None
+    except Exception as exc:
+        raise RuntimeError(
+            f"the fused all-reduce engine could not be set up ({type(exc).__name__}: {exc}); "
+            "set NT_FUSED_ALLREDUCE=0 to run the NCCL all-reduce on purpose") from exc

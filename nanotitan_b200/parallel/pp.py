@@ -120,6 +120,10 @@ class PipelineParallel:
         self._pending.append((tensor, dist.isend(tensor.contiguous(), dst=dst, group=self.dim.pp_group)))
 
     def _zero_grad(self, optimizer) -> None:
+        if self.device.type == "cuda" and self.dim.ep_size > 1:
+            from nanotitan_b200.parallel import ep_fused
+
+            ep_fused.reset_pools()  # staging buffers of layers whose backward never ran
         owned = {id(p) for r in self.reducers.values() for p in r.params}
         lazy = self.device.type == "cuda"  # native kernels write first gradients into their bucket slots
         for r in self.reducers.values():

@@ -203,3 +203,34 @@ def test_recorded_failure_turns_later_kernels_into_noops_until_cleared():
     assert ext.read_status(True)[0] == 1
     native.gemm_tc(x, False, [x[:64].contiguous()], False, [y])
     assert not (y == 7.0).all()
+
+
+@pytest.mark.gpu
+def test_cross_rank_barrier_wait_runs_out_on_one_gpu():
+    """The flag barrier of the expert-parallel kernels, made to give up without a second GPU and without
+    any rank leaving: a two-entry peer table whose entries both point at this GPU's own flag pad, and a
+    "peer" word that nobody ever writes.  The kernel returns after its 50 ms limit, the status word says
+    time-out in the dispatch kernel, and the next kernel runs normally."""
+    from nanotitan_b200.ops.ext import get_ext
+
+    ext = get_ext()
+    ext.read_status(True)
+    dev = torch.device("cuda", 0)
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)
+    cmat = torch.zeros(2, 4, dtype=torch.int32, device=dev)
+    counts = torch.tensor([1, 2, 3, 4], dtype=torch.int32, device=dev)
+    epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+    both_me = torch.tensor([flags.data_ptr(), flags.data_ptr()], dtype=torch.int64)
+    cmat_me = torch.tensor([cmat.data_ptr(), cmat.data_ptr()], dtype=torch.int64)
+    start = time.perf_counter()
+    ext.ep_allgather_counts(counts, cmat_me, flags, both_me, 0, 2, epoch, 0, 50.0)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - start < 5.0
+    code, kernel, detail, count = ext.read_status(True)
+    assert (code, kernel) == (1, 5) and count >= 1 and detail % 1000 == 1, (code, kernel, detail, count)
+    assert int(epoch.item()) == 1  # the launch still advanced its epoch: later launches stay in step
+    # the context is intact and later kernels are not no-ops once the word is cleared
+    y = torch.empty(8, dtype=torch.float32, device=dev)
+    ext.copy_vector(torch.arange(8, dtype=torch.float32, device=dev), y)
+    assert y.tolist() == list(range(8))
+    assert ext.read_status(True)[0] == 0
