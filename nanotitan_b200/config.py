@@ -53,6 +53,9 @@ class RuntimeConfig(_Strict):
     pp_size: int = 1
     ep_size: int = 1
     num_expert: PositiveInt = 1  # mirrored from model.num_experts by AppConfig
+    # Capture the whole optimizer step in a CUDA graph after two ordinary steps (GPU, pp_size 1);
+    # the environment variable NT_CUDA_GRAPH=0/1 overrides it.  No counterpart in the reference.
+    cuda_graph: bool = True
 
 
 class ProfilerConfig(_Strict):

@@ -22,7 +22,7 @@
 // load/store/reduce instructions on a multicast address.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
-#include <torch/extension.h>
+#include <ATen/ATen.h>
 
 #include "cuda_check.h"
 #include "ops.h"

@@ -4,7 +4,7 @@
 // bound to Python.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
-#include <torch/extension.h>
+#include <ATen/ATen.h>
 
 #include "cuda_check.h"
 #include "ops.h"

@@ -7,7 +7,7 @@
 // caller in a fixed order.  Columns >= V (row padding kept for TMA alignment) are zeroed.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
-#include <torch/extension.h>
+#include <ATen/ATen.h>
 
 #include "cuda_check.h"
 #include "ops.h"

@@ -22,7 +22,7 @@
 // each other's MMA and exponential phases.  Every mbarrier wait is bounded (see sm100.cuh).
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
-#include <torch/extension.h>
+#include <ATen/ATen.h>
 
 #include "cuda_check.h"
 #include "ops.h"
@@ -33,7 +33,7 @@
 #include <type_traits>
 
 namespace nt {
-namespace flash {
+namespace attn {
 
 enum Mode : int { kFwd = 0, kDq = 1, kDkv = 2 };
 constexpr int BR = 128;  // resident rows
@@ -132,7 +132,7 @@ __device__ __forceinline__ void store_row(void* base, long long off, const float
 // DT: 0 = fp16, 1 = bf16 (compile-time so the pack / convert code has no per-element selects)
 template <int DH, int MODE, int DT>
 __global__ void __launch_bounds__(THREADS, 2)
-flash_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1,
+causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constant__ CUtensorMap tm1,
              const __grid_constant__ CUtensorMap tm2, const __grid_constant__ CUtensorMap tm3, const Args args) {
   using namespace sm100;
   using C = Cfg<DH, MODE>;
@@ -573,21 +573,21 @@ void launch(const CUtensorMap& m0, const CUtensorMap& m1, const CUtensorMap& m2,
   using C = Cfg<DH, MODE>;
   static bool configured = false;
   if (!configured) {
-    NT_CUDA_CHECK(cudaFuncSetAttribute(flash_kernel<DH, MODE, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
-    NT_CUDA_CHECK(cudaFuncSetAttribute(flash_kernel<DH, MODE, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
+    NT_CUDA_CHECK(cudaFuncSetAttribute(causal_attn_kernel<DH, MODE, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
+    NT_CUDA_CHECK(cudaFuncSetAttribute(causal_attn_kernel<DH, MODE, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
     configured = true;
   }
   dim3 grid((a.S + BR - 1) / BR, a.H, a.B);
-  if (a.dtype == 1) flash_kernel<DH, MODE, 1><<<grid, THREADS, C::TOTAL, stream>>>(m0, m1, m2, m3, a);
-  else flash_kernel<DH, MODE, 0><<<grid, THREADS, C::TOTAL, stream>>>(m0, m1, m2, m3, a);
-  NT_KERNEL_CHECK();
+  if (a.dtype == 1) causal_attn_kernel<DH, MODE, 1><<<grid, THREADS, C::TOTAL, stream>>>(m0, m1, m2, m3, a);
+  else causal_attn_kernel<DH, MODE, 0><<<grid, THREADS, C::TOTAL, stream>>>(m0, m1, m2, m3, a);
+  NT_KERNEL_CHECK_AS(MODE == kFwd ? "causal_attn_kernel<fwd>" : (MODE == kDq ? "causal_attn_kernel<dq>" : "causal_attn_kernel<dkv>"));
 }
 
-}  // namespace flash
+}  // namespace attn
 
 // q, k, v: [B, S, H, Dh] -> (out [B, S, H, Dh], lse [B, H, S] fp32)
 std::vector<at::Tensor> flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale) {
-  using namespace flash;
+  using namespace attn;
   check_bshd(q, "q"); check_bshd(k, "k"); check_bshd(v, "v");
   TORCH_CHECK(q.sizes() == k.sizes() && q.sizes() == v.sizes() && q.scalar_type() == k.scalar_type() && q.scalar_type() == v.scalar_type(), "q, k, v must match");
   c10::cuda::CUDAGuard guard(q.device());
@@ -612,7 +612,7 @@ std::vector<at::Tensor> flash_fwd(const at::Tensor& q, const at::Tensor& k, cons
 // thirds of one fused dQKV buffer) that receive dq, dk, dv.
 std::vector<at::Tensor> flash_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                   const at::Tensor& out, const at::Tensor& lse, double scale, const std::vector<at::Tensor>& grads) {
-  using namespace flash;
+  using namespace attn;
   check_bshd(q, "q"); check_bshd(k, "k"); check_bshd(v, "v"); check_bshd(dout, "dout"); check_bshd(out, "out");
   TORCH_CHECK(dout.is_contiguous() && out.is_contiguous(), "dout and out must be contiguous");
   c10::cuda::CUDAGuard guard(q.device());

@@ -1,7 +1,7 @@
 // Host side of the tcgen05 GEMM: shape bookkeeping, TMA descriptors, tile-size choice, launch.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
-#include <torch/extension.h>
+#include <ATen/ATen.h>
 
 #include <cstdlib>
 #include <cstring>
@@ -78,7 +78,7 @@ void launch(const CUtensorMap& tA, const CUtensorMap (&tB)[3], const CUtensorMap
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   const int grid = std::max(1, std::min(tiles, sms));
   kernel<<<grid, gemm::NUM_THREADS, S::TOTAL, stream>>>(tA, tB[0], tB[1], tB[2], tC[0], tC[1], tC[2], args);
-  NT_KERNEL_CHECK();
+  NT_KERNEL_CHECK_AS("gemm_tc_kernel");
 }
 
 template <int EPI>
@@ -93,7 +93,7 @@ void launch_pair(const CUtensorMap& tA, const CUtensorMap (&tB)[3], const CUtens
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount & ~1;
   const int grid = std::max(2, std::min(2 * tiles, sms));
   kernel<<<grid, gemm::NUM_THREADS, gemm::PAIR_SMEM, stream>>>(tA, tB[0], tB[1], tB[2], tC[0], tC[1], tC[2], args);  // clusters of 2 (compile-time attribute)
-  NT_KERNEL_CHECK();
+  NT_KERNEL_CHECK_AS("gemm_tc_pair_kernel");
 }
 
 bool pair_kernels_enabled() {
@@ -424,7 +424,7 @@ void gemm_tc(const at::Tensor& A, bool a_mn, const std::vector<at::Tensor>& Bs, 
     splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(args.ws, args.k_splits, part, args.M, args.N, args.C[0], args.C[1], args.C[2],
                                                      args.ldc, args.c_group_stride, args.c_split_size, args.out_f32, args.dtype,
                                                      args.accumulate);
-    NT_KERNEL_CHECK();
+    NT_KERNEL_CHECK_AS("splitk_reduce_kernel");
   }
 }
 

@@ -4,7 +4,7 @@
 // on the host: the reference's wrappers do 2*E blocking device-to-host reads per call
 // (csrc/kernels/grouped_gemm.cu:58-62).
 #include <c10/cuda/CUDAGuard.h>
-#include <torch/extension.h>
+#include <ATen/ATen.h>
 
 #include "gemm_tc.cuh"
 #include "ops.h"

@@ -2,6 +2,8 @@
 // for callers that cannot allocate.  Self-contained on purpose (CUDA runtime only, no PyTorch).
 #include "ln_bwd_noalloc.h"
 
+#include <atomic>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -94,15 +96,18 @@ int fail(int code, const char* what, char* err, int err_len) {
 
 // Device address of g_scratch, looked up once per device.  In host code the name `g_scratch` is only
 // a handle for the runtime; the address a kernel can use comes from cudaGetSymbolAddress.
+// Host threads may make their first calls at the same time: the entries are atomics, and two threads
+// that both find an entry empty both look the address up and store the same value.
 float* scratch_for_current_device(char* err, int err_len, int* rc) {
-  static float* table[64] = {nullptr};
+  static std::atomic<float*> table[64];  // zero-initialised (static storage)
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= 64) {
     *rc = fail(NT_LN_NOALLOC_CUDA_ERROR, "nt_layer_norm_bwd_noalloc: cudaGetDevice failed", err, err_len);
     return nullptr;
   }
-  if (table[dev] == nullptr) {
+  float* known = table[dev].load(std::memory_order_acquire);
+  if (known == nullptr) {
     float* ptr = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_scratch);
     if (e != cudaSuccess || ptr == nullptr) {
@@ -111,9 +116,10 @@ float* scratch_for_current_device(char* err, int err_len, int* rc) {
       *rc = fail(NT_LN_NOALLOC_CUDA_ERROR, msg, err, err_len);
       return nullptr;
     }
-    table[dev] = ptr;
+    table[dev].store(ptr, std::memory_order_release);
+    known = ptr;
   }
-  return table[dev];
+  return known;
 }
 
 template <typename T>

@@ -16,7 +16,9 @@
 //     the library, until the process exits.
 //   * The first call on a device looks up the device address of the scratch array
 //     (cudaGetSymbolAddress).  Make that first call outside any stream capture, with the device
-//     that owns the buffers current.
+//     that owns the buffers current.  Several host threads may make their first calls at the same
+//     time (the per-device address cache is atomic); the cache is keyed by device ordinal and
+//     assumes the device is not reset (cudaDeviceReset) while the library stays loaded.
 //   * All calls share the one scratch array, and it keeps what the previous call left in it; the
 //     kernel clears the part it uses.  Two calls whose kernels overlap on the GPU (different
 //     streams, no dependency between them) race on it: order them.

@@ -10,9 +10,15 @@
 // Token -> rows maps are given either as a fixed fan-out (`slot_of [T,k]`) or in CSR form
 // (`row_start [T+1]`, `rows [A]`), which is what the reference-style entry points build from
 // an arbitrary `packed_tokenId`.
+//
+// Every index read from a map (a slot, a packed row, a token id) is range-checked before it is used
+// as an address: an index outside its tensor is skipped and recorded in the device status word
+// (kernel id, offending value) instead of faulting, so a corrupted routing table surfaces as a
+// Python exception at the end of the step.  The checks are compares on values the kernels load
+// anyway; they are always compiled in.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
-#include <torch/extension.h>
+#include <ATen/ATen.h>
 
 #include "cuda_check.h"
 #include "ops.h"
@@ -29,20 +35,29 @@ template <typename T, int VEC>
 __global__ void __launch_bounds__(PK_WARPS * 32)
 pack_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gates, const int* __restrict__ idx,
                 const int* __restrict__ slot_of, T* __restrict__ packed_x, int* __restrict__ packed_token,
-                int* __restrict__ packed_expert, float* __restrict__ packed_gate, long long tokens, int d, int k) {
+                int* __restrict__ packed_expert, float* __restrict__ packed_gate, long long tokens, int d, int k,
+                StatusWord* __restrict__ status) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long t = static_cast<long long>(blockIdx.x) * PK_WARPS + warp;
   if (t >= tokens) return;
+  const long long A = tokens * k;
   if (lane < k) {
     const int s = slot_of[t * k + lane];
-    packed_token[s] = static_cast<int>(t);
-    packed_expert[s] = idx[t * k + lane];
-    packed_gate[s] = gates[t * k + lane];
+    if (s < 0 || s >= A) {
+      report_status(status, kStatusBounds, kKernelPack, static_cast<uint32_t>(s));
+    } else {
+      packed_token[s] = static_cast<int>(t);
+      packed_expert[s] = idx[t * k + lane];
+      packed_gate[s] = gates[t * k + lane];
+    }
   }
   for (int c = lane * VEC; c < d; c += 32 * VEC) {
     float v[VEC];
     load_vec<T, VEC>(x + t * d + c, v);
-    for (int j = 0; j < k; ++j) store_vec<T, VEC>(packed_x + static_cast<long long>(slot_of[t * k + j]) * d + c, v);
+    for (int j = 0; j < k; ++j) {
+      const long long s = slot_of[t * k + j];
+      if (s >= 0 && s < A) store_vec<T, VEC>(packed_x + s * d + c, v);
+    }
   }
 }
 
@@ -51,7 +66,7 @@ template <typename T, typename OutT, int VEC>
 __global__ void __launch_bounds__(PK_WARPS * 32)
 combine_fwd_kernel(const T* __restrict__ y, const float* __restrict__ w, const int* __restrict__ rows,
                    const int* __restrict__ row_start, int k_fixed, const T* __restrict__ residual,
-                   OutT* __restrict__ out, long long tokens, int d) {
+                   OutT* __restrict__ out, long long tokens, int d, long long y_rows, StatusWord* __restrict__ status) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long t = static_cast<long long>(blockIdx.x) * PK_WARPS + warp;
   if (t >= tokens) return;
@@ -67,6 +82,10 @@ combine_fwd_kernel(const T* __restrict__ y, const float* __restrict__ w, const i
     }
     for (long long a = lo; a < hi; ++a) {
       const int r = rows[a];
+      if (r < 0 || r >= y_rows) {
+        if (c == 0) report_status(status, kStatusBounds, kKernelCombine, static_cast<uint32_t>(r));
+        continue;
+      }
       const float g = w[r];
       float v[VEC];
       load_vec<T, VEC>(y + static_cast<long long>(r) * d + c, v);
@@ -81,11 +100,19 @@ combine_fwd_kernel(const T* __restrict__ y, const float* __restrict__ w, const i
 template <typename T, typename GT, int VEC>
 __global__ void __launch_bounds__(PK_WARPS * 32)
 combine_bwd_kernel(const T* __restrict__ y, const int* __restrict__ token, const float* __restrict__ w,
-                   const GT* __restrict__ dout, T* __restrict__ dy, float* __restrict__ dw, long long assignments, int d) {
+                   const GT* __restrict__ dout, T* __restrict__ dy, float* __restrict__ dw, long long assignments, int d,
+                   long long tokens, StatusWord* __restrict__ status) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long a = static_cast<long long>(blockIdx.x) * PK_WARPS + warp;
   if (a >= assignments) return;
   const long long t = token[a];
+  if (t < 0 || t >= tokens) {
+    if (lane == 0) {
+      report_status(status, kStatusBounds, kKernelCombine, static_cast<uint32_t>(t));
+      dw[a] = 0.f;
+    }
+    return;
+  }
   const float g = w[a];
   float dot = 0.f;
   for (int c = lane * VEC; c < d; c += 32 * VEC) {
@@ -107,7 +134,7 @@ combine_bwd_kernel(const T* __restrict__ y, const int* __restrict__ token, const
 template <typename T, int VEC>
 __global__ void __launch_bounds__(PK_WARPS * 32)
 pack_bwd_kernel(const T* __restrict__ dpacked, const int* __restrict__ rows, const int* __restrict__ row_start, int k_fixed,
-                T* __restrict__ dx, long long tokens, int d) {
+                T* __restrict__ dx, long long tokens, int d, long long packed_rows, StatusWord* __restrict__ status) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long t = static_cast<long long>(blockIdx.x) * PK_WARPS + warp;
   if (t >= tokens) return;
@@ -119,7 +146,12 @@ pack_bwd_kernel(const T* __restrict__ dpacked, const int* __restrict__ rows, con
     for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
     for (long long a = lo; a < hi; ++a) {
       float v[VEC];
-      load_vec<T, VEC>(dpacked + static_cast<long long>(rows[a]) * d + c, v);
+      const long long r = rows[a];
+      if (r < 0 || r >= packed_rows) {
+        if (c == 0) report_status(status, kStatusBounds, kKernelPack, static_cast<uint32_t>(r));
+        continue;
+      }
+      load_vec<T, VEC>(dpacked + r * d + c, v);
 #pragma unroll
       for (int i = 0; i < VEC; ++i) acc[i] += v[i];
     }
@@ -179,7 +211,8 @@ std::vector<at::Tensor> pack_fwd(const at::Tensor& x, const at::Tensor& gates, c
     constexpr int V = 16 / sizeof(scalar_t);
     auto run = [&](auto kernel) {
       kernel<<<grid, PK_WARPS * 32, 0, stream>>>(x.data_ptr<scalar_t>(), gates.data_ptr<float>(), idx.data_ptr<int>(), slot_of.data_ptr<int>(),
-          packed_x.data_ptr<scalar_t>(), packed_token.data_ptr<int>(), packed_expert.data_ptr<int>(), packed_gate.data_ptr<float>(), tokens, d, k);
+          packed_x.data_ptr<scalar_t>(), packed_token.data_ptr<int>(), packed_expert.data_ptr<int>(), packed_gate.data_ptr<float>(), tokens, d, k,
+          device_status_word());
     };
     if (vec_ok(d, sizeof(scalar_t), {x.data_ptr(), packed_x.data_ptr()})) run(pack_fwd_kernel<scalar_t, V>);
     else run(pack_fwd_kernel<scalar_t, 1>);
@@ -207,7 +240,8 @@ at::Tensor combine_fwd(const at::Tensor& y, const at::Tensor& w, const at::Tenso
     const scalar_t* res = residual.has_value() ? residual->data_ptr<scalar_t>() : nullptr;
     const bool vec = vec_ok(d, sizeof(scalar_t), {y.data_ptr(), res}) && (out_f32 ? d % 4 == 0 : true) && is_aligned16(out.data_ptr());
     auto run = [&](auto kernel, auto* outp) {
-      kernel<<<grid, PK_WARPS * 32, 0, stream>>>(y.data_ptr<scalar_t>(), w.data_ptr<float>(), rows.data_ptr<int>(), rs, k_fixed, res, outp, tokens, d);
+      kernel<<<grid, PK_WARPS * 32, 0, stream>>>(y.data_ptr<scalar_t>(), w.data_ptr<float>(), rows.data_ptr<int>(), rs, k_fixed, res, outp, tokens, d,
+                                                 static_cast<long long>(y.size(0)), device_status_word());
     };
     if (out_f32) {
       // fp32 rows are written 4 elements per 16-byte store; keep the scalar path for simplicity
@@ -242,12 +276,12 @@ std::vector<at::Tensor> combine_bwd(const at::Tensor& y, const at::Tensor& token
     if (same) {
       auto run = [&](auto kernel) {
         kernel<<<grid, PK_WARPS * 32, 0, stream>>>(y.data_ptr<scalar_t>(), token.data_ptr<int>(), w.data_ptr<float>(), dout.data_ptr<scalar_t>(),
-            dy.data_ptr<scalar_t>(), dw.data_ptr<float>(), A, d);
+            dy.data_ptr<scalar_t>(), dw.data_ptr<float>(), A, d, static_cast<long long>(dout.size(0)), device_status_word());
       };
       if (vec) run(combine_bwd_kernel<scalar_t, scalar_t, V>); else run(combine_bwd_kernel<scalar_t, scalar_t, 1>);
     } else {
       combine_bwd_kernel<scalar_t, float, 1><<<grid, PK_WARPS * 32, 0, stream>>>(y.data_ptr<scalar_t>(), token.data_ptr<int>(), w.data_ptr<float>(),
-          dout.data_ptr<float>(), dy.data_ptr<scalar_t>(), dw.data_ptr<float>(), A, d);
+          dout.data_ptr<float>(), dy.data_ptr<scalar_t>(), dw.data_ptr<float>(), A, d, static_cast<long long>(dout.size(0)), device_status_word());
     }
   });
   NT_KERNEL_CHECK();
@@ -267,7 +301,8 @@ at::Tensor pack_bwd(const at::Tensor& dpacked, const at::Tensor& rows, const c10
   NT_DISPATCH_FLOAT(dpacked.scalar_type(), "pack_bwd", [&] {
     constexpr int V = 16 / sizeof(scalar_t);
     auto run = [&](auto kernel) {
-      kernel<<<grid, PK_WARPS * 32, 0, stream>>>(dpacked.data_ptr<scalar_t>(), rows.data_ptr<int>(), rs, k_fixed, dx.data_ptr<scalar_t>(), tokens, d);
+      kernel<<<grid, PK_WARPS * 32, 0, stream>>>(dpacked.data_ptr<scalar_t>(), rows.data_ptr<int>(), rs, k_fixed, dx.data_ptr<scalar_t>(), tokens, d,
+                                                 static_cast<long long>(dpacked.size(0)), device_status_word());
     };
     if (vec_ok(d, sizeof(scalar_t), {dpacked.data_ptr(), dx.data_ptr()})) run(pack_bwd_kernel<scalar_t, V>); else run(pack_bwd_kernel<scalar_t, 1>);
   });

@@ -10,7 +10,7 @@
 //  * count_experts: the standalone histogram with optional mask of the reference's API.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
-#include <torch/extension.h>
+#include <ATen/ATen.h>
 
 #include "cuda_check.h"
 #include "ops.h"

@@ -1,6 +1,6 @@
 // Host entry points of the extension (one declaration per kernel family).
 #pragma once
-#include <torch/extension.h>
+#include <ATen/ATen.h>
 
 #include <string>
 #include <vector>

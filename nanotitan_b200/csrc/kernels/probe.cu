@@ -4,7 +4,7 @@
 // and NVLink kernels are exercised without faulting, trapping or hanging the GPU.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
-#include <torch/extension.h>
+#include <ATen/ATen.h>
 
 #include "cuda_check.h"
 #include "ops.h"

@@ -60,6 +60,14 @@ inline LaunchSites& launch_sites() {
     ::nt::launch_counter().fetch_add(1);                   \
     NT_CUDA_CHECK(cudaGetLastError());                     \
   } while (0)
+// Same, filed under an explicit name (for launches made from helper templates or lambdas).
+#define NT_KERNEL_CHECK_AS(NAME)                           \
+  do {                                                     \
+    static std::atomic<long long>& nt_site_ = ::nt::launch_sites().at(NAME); \
+    nt_site_.fetch_add(1);                                 \
+    ::nt::launch_counter().fetch_add(1);                   \
+    NT_CUDA_CHECK(cudaGetLastError());                     \
+  } while (0)
 // Names kept for code written against the reference's macros.
 #define CUDA_CHECK(expr) NT_CUDA_CHECK(expr)
 #define CUDA_KERNEL_CHECK() NT_KERNEL_CHECK()

@@ -26,6 +26,8 @@ enum KernelId : uint32_t {
   kKernelEpDispatch = 5,
   kKernelEpCombine = 6,
   kKernelProbe = 7,
+  kKernelPack = 8,
+  kKernelCombine = 9,
 };
 
 #ifdef __CUDACC__

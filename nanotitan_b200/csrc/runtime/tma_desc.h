@@ -80,7 +80,13 @@ inline CUtensorMap make_tma_desc_sw(const void* base, int elem_bytes, int rank, 
   if (swizzle_bytes && static_cast<int>(box[0]) * elem_bytes > swizzle_bytes) throw std::runtime_error("TMA: inner box exceeds the swizzle span");
   // The encoder is a driver call: make sure this thread (e.g. an autograd worker) has the
   // device's primary context bound before calling it.
-  NT_CUDA_CHECK(cudaFree(nullptr));
+  // Once per thread: the call is not allowed while a stream capture is open, and warm-up steps
+  // have made it on every thread that launches kernels by then.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    NT_CUDA_CHECK(cudaFree(nullptr));
+    context_bound = true;
+  }
   if ((box[0] * elem_bytes) % 16 != 0) throw std::runtime_error("TMA: inner box extent not a multiple of 16 bytes");
   CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                            : elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32

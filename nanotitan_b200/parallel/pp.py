@@ -12,10 +12,22 @@ What differs: stage-boundary activations travel with non-blocking NCCL `isend` /
 backward), so transfers of microbatch i+1 overlap the compute of microbatch i; the
 last stage computes the loss with the fused unembed + cross-entropy op; times are
 CUDA-event device times; and there is one device sync per step, at its end.
+
+CUDA graph.  A step launches several thousand kernels, many of them a few microseconds
+long, so the host, not the GPU, sets the pace of small models (and with expert parallelism
+every cross-rank barrier then waits for the slowest host).  On GPUs with `pp_size == 1`
+the step - zero-grad, forward, loss, backward with the bucket kernels on their side
+stream, optimizer update - is therefore captured into one CUDA graph after two ordinary
+steps and replayed from then on: one launch per step.  Everything that changes from step
+to step lives in device memory (token ids in static input buffers, AdamW bias corrections
+in a two-float tensor staged before each replay, the epochs of the cross-rank barriers in
+counters the kernels advance themselves), so the captured launches never need new
+arguments.  `runtime.cuda_graph = false` or `NT_CUDA_GRAPH=0` keeps the step eager.
 """
 from __future__ import annotations
 
 import logging
+import os
 import time
 
 import torch
@@ -46,6 +58,8 @@ class _Clock:
 
     def seconds(self, start: str, end: str) -> float:
         a, b = self.marks[start], self.marks[end]
+        if a is None or b is None:
+            return 0.0
         if self.cuda:
             return a.elapsed_time(b) / 1e3
         return b - a
@@ -65,6 +79,23 @@ class PendingMetrics:
         return self._metrics
 
 
+class _StepGraph:
+    """A captured step: static inputs, the graph, and its static metric outputs."""
+
+    def __init__(self):
+        self.graph = None
+        self.x = self.y = None
+        self.floats = None      # [ce_sum, aux_sum, routing counts...] written by every replay
+        self.n_local = 0
+        self.key = None
+        self.launches = 0       # kernels of this library recorded in the graph
+        self.launches_by_kernel: dict = {}
+        self.inner_marks: dict = {}
+
+
+EAGER_STEPS_BEFORE_CAPTURE = 2
+
+
 class PipelineParallel:
     def __init__(self, cfg, dim, reducers: dict):
         self.cfg = cfg
@@ -75,6 +106,12 @@ class PipelineParallel:
         self.stage_outputs: list[torch.Tensor] = []
         self._pending: list = []
         self.use_fused_loss = True
+        env = os.environ.get("NT_CUDA_GRAPH")
+        want = getattr(cfg.runtime, "cuda_graph", True) if env is None else env != "0"
+        self.graph_enabled = bool(want) and self.device.type == "cuda" and dim.pp_size == 1
+        self._graph: _StepGraph | None = None
+        self._eager_steps = 0
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ helpers
     def synchronize_device(self) -> None:
@@ -141,14 +178,41 @@ class PipelineParallel:
         the losses, routing counts and kernel status travel to pinned host memory behind the step,
         and `.result()` waits for that step alone - call it after launching the next step and the
         host never stalls the device."""
+        if self._graphable(model, batch, optimizer):
+            return self._graphed_step(model, batch, optimizer, collect_metrics)
+        return self._eager_step(model, batch, optimizer, collect_metrics)
+
+    def _eager_step(self, model, batch, optimizer, collect_metrics):
         x, y = batch
+        n_mb = self.cfg.runtime.num_microbatches
+        clock = _Clock(self.device)
+        host_start = time.perf_counter()
+        clock.mark("start")
+        if getattr(optimizer, "_bc_dev", None) is not None:
+            optimizer.stage_step_constants()
+        ce_losses, aux_losses, stats_list = self._run(model, x, y, optimizer, clock)
+        clock.mark("end")
+        for _, work in self._pending:
+            work.wait()
+        self._pending = []
+        self._eager_steps += 1
+        if not collect_metrics:
+            return None
+        floats, n_local = self._metric_floats(ce_losses, aux_losses, stats_list)
+        pending = self._start_metrics(model, floats, n_local, clock, host_start, n_mb)
+        return pending if collect_metrics == "deferred" else pending.result()
+
+    def _run(self, model, x, y, optimizer, clock):
+        """zero-grad, all forwards, all backwards, gradient sync, optimizer update.  `clock` may be
+        None (inside a graph capture, where ordinary timing events cannot be recorded)."""
         n_mb = self.cfg.runtime.num_microbatches
         microbatch_x, microbatch_y = self.prepare_microbatch(x, y)
         self.microbatch_size = x.shape[0] // n_mb
         first, last = self.dim.is_pp_first_stage, self.dim.is_pp_last_stage
-        clock = _Clock(self.device)
-        host_start = time.perf_counter()
-        clock.mark("start")
+
+        def mark(name):
+            if clock is not None:
+                clock.mark(name)
 
         self._zero_grad(optimizer)
         ce_losses, aux_losses, stats_list = [], [], []
@@ -180,7 +244,7 @@ class PipelineParallel:
                 aux = torch.stack([s.aux_loss for s in stats]).mean() / self.dim.pp_size
                 aux_losses.append(aux)
                 stats_list.append(stats)
-        clock.mark("forward_end")
+        mark("forward_end")
 
         with nvtx_range("backward_pass"):
             grads_in = [] if last else self._post_recvs(self.dim.next_pp_rank, n_mb)
@@ -194,22 +258,92 @@ class PipelineParallel:
             for reducer in self.reducers.values():
                 reducer.prepare_missing_grad()
             self.finalize_backward()
-        clock.mark("backward_end")
+        mark("backward_end")
 
         with nvtx_range("optimizer_step"):
             optimizer.step()
+        return ce_losses, aux_losses, stats_list
+
+    # ------------------------------------------------------------------ CUDA graph
+    def _graphable(self, model, batch, optimizer) -> bool:
+        if not self.graph_enabled or not hasattr(optimizer, "enable_device_constants"):
+            return False
+        if not (self.use_fused_loss and hasattr(model, "forward_loss")):
+            return False
+        if self._graph is not None:
+            return self._graph.key == self._graph_key(model, batch, optimizer)
+        return self._eager_steps >= EAGER_STEPS_BEFORE_CAPTURE
+
+    @staticmethod
+    def _graph_key(model, batch, optimizer):
+        x, y = batch
+        return (id(model), id(optimizer), tuple(x.shape), tuple(y.shape), x.dtype, y.dtype)
+
+    def _capture(self, model, batch, optimizer) -> _StepGraph:
+        """Record one whole step into a CUDA graph.  Nothing executes during the capture; the caller
+        replays the graph to actually take the step."""
+        from nanotitan_b200.ops import ext
+
+        x, y = batch
+        g = _StepGraph()
+        g.key = self._graph_key(model, batch, optimizer)
+        g.x = torch.empty(x.shape, dtype=x.dtype, device=self.device)
+        g.y = torch.empty(y.shape, dtype=y.dtype, device=self.device)
+        g.x.copy_(x)
+        g.y.copy_(y)
+        optimizer.enable_device_constants(self.device)
+        optimizer.stage_step_constants()
+        native = ext.get_ext() if ext.have_ext() else None
+        torch.cuda.synchronize(self.device)
+        before, before_by = (native.launch_count(), native.launch_counts()) if native else (0, {})
+        step_before = optimizer._step
+        g.graph = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(g.graph):
+                ce_losses, aux_losses, stats_list = self._run(model, g.x, g.y, optimizer, None)
+                g.floats, g.n_local = self._metric_floats(ce_losses, aux_losses, stats_list)
+        except Exception as exc:
+            raise RuntimeError(
+                f"capturing the training step in a CUDA graph failed ({type(exc).__name__}: {exc}); "
+                "set NT_CUDA_GRAPH=0 (or runtime.cuda_graph = false) to run the step eagerly") from exc
+        optimizer._step = step_before  # the capture ran optimizer.step()'s bookkeeping, not the update
+        if native:
+            g.launches = native.launch_count() - before
+            g.launches_by_kernel = {k: v - before_by.get(k, 0) for k, v in native.launch_counts().items()
+                                    if v - before_by.get(k, 0)}
+        logger.info("training step captured in a CUDA graph (%d kernels of this library per replay)", g.launches)
+        return g
+
+    def _graphed_step(self, model, batch, optimizer, collect_metrics):
+        if self._graph is None:
+            self._graph = self._capture(model, batch, optimizer)
+        g = self._graph
+        x, y = batch
+        n_mb = self.cfg.runtime.num_microbatches
+        clock = _Clock(self.device)
+        host_start = time.perf_counter()
+        clock.mark("start")
+        g.x.copy_(x, non_blocking=True)  # from pinned host memory: the step's host-to-device copy
+        g.y.copy_(y, non_blocking=True)
+        optimizer.stage_step_constants()
+        g.graph.replay()
+        optimizer._step += 1
+        self.graph_replays += 1
         clock.mark("end")
-        for _, work in self._pending:
-            work.wait()
-        self._pending = []
+        clock.marks["forward_end"] = clock.marks["backward_end"] = None  # not separable inside a graph
         if not collect_metrics:
             return None
-        pending = self._start_metrics(model, ce_losses, aux_losses, stats_list, clock, host_start, n_mb)
+        pending = self._start_metrics(model, g.floats, g.n_local, clock, host_start, n_mb)
         return pending if collect_metrics == "deferred" else pending.result()
 
-    def _start_metrics(self, model, ce_losses, aux_losses, stats_list, clock, host_start, n_mb) -> "PendingMetrics":
-        """Pack everything the step's metrics need from the device (losses, routing counts, the
-        kernels' status word) into two stream-ordered copies to pinned host memory."""
+    def launches_last_step(self) -> tuple[int, dict]:
+        """(kernels of this library, by entry point) a replayed step runs; (0, {}) while eager."""
+        if self._graph is None:
+            return 0, {}
+        return self._graph.launches, dict(self._graph.launches_by_kernel)
+
+    def _metric_floats(self, ce_losses, aux_losses, stats_list):
+        """One fp32 device tensor [ce_sum, aux_sum, routing counts of the local layers...]."""
         last = self.dim.is_pp_last_stage
         zero = torch.zeros((), dtype=torch.float32, device=self.device)
         ce_sum = torch.stack([c.detach().float() for c in ce_losses]).sum() if last else zero
@@ -221,7 +355,11 @@ class PipelineParallel:
                 [torch.stack([mb[i].tokens_per_expert.detach().float() for i in range(n_local)]) for mb in stats_list]
             ).sum(dim=0)  # [local layers, E]
             parts.append(counts.reshape(-1))
-        floats = torch.cat(parts)
+        return torch.cat(parts), n_local
+
+    def _start_metrics(self, model, floats, n_local, clock, host_start, n_mb) -> "PendingMetrics":
+        """Send everything the step's metrics need from the device (losses and routing counts in
+        `floats`, the kernels' status word) to pinned host memory with two stream-ordered copies."""
         status = None
         if self.device.type == "cuda":
             from nanotitan_b200.ops import ext
@@ -251,6 +389,7 @@ class PipelineParallel:
             # same precedence as the reference: sum(ce) + sum(aux)/n (src/parallel/pp.py:124)
             "train/total_loss": ScalarMetric(ce_sum + aux_sum / n_mb if last else 0.0, reduce="sum"),
             "time/step_time": ScalarMetric(clock.seconds("start", "end"), reduce="max"),
+            # a replayed graph has no host-visible boundary between forward and backward: 0.0 there
             "time/forward_time": ScalarMetric(clock.seconds("start", "forward_end"), reduce="max"),
             "time/backward_time": ScalarMetric(clock.seconds("forward_end", "backward_end"), reduce="max"),
             "time/host_step_time": ScalarMetric(time.perf_counter() - pending.host_start, reduce="max"),
