@@ -257,7 +257,8 @@ def run_ours(args, config: str) -> dict:
     batch, seed = BATCH[config], SEEDS[config]
     cfg = AppConfig.model_validate(dict(
         run_name="bench", max_steps=1_000_000, model=model_kw,
-        trainer=dict(device_id=0, eval_every_step=-1, per_device_batch_size=batch, seed=seed),
+        # weights: trainer seed (the reference's schema wants it > 0); token ids: `seed` itself
+        trainer=dict(device_id=0, eval_every_step=-1, per_device_batch_size=batch, seed=seed or 1),
         data=dict(num_workers=1, train_tokens_path="unused", val_tokens_path="unused"),
         optim=dict(type="adam", lr=LR),
         runtime=dict(name="bench", dp_size=dp, pp_size=pp, ep_size=ep, num_microbatches=MICROBATCHES[config],
@@ -265,7 +266,7 @@ def run_ours(args, config: str) -> dict:
     ))
     init_distributed()
     device = local_device()
-    seed_everything(seed)
+    seed_everything(seed or 1)
     dims = get_parallel_dims(cfg.runtime)
     model, dp_wrap, step, optimizer = build_training(cfg, dims)
     reducers = dp_wrap.get_reducers()
@@ -376,7 +377,7 @@ def run_reference(args, config: str) -> dict:
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
         dist.init_process_group(backend="nccl", init_method="env://")
     cfg, dims, model, step, optimizer = ref_harness.build(
-        MODELS[config], batch, dp, pp, ep, MICROBATCHES[config], LR, seed)
+        MODELS[config], batch, dp, pp, ep, MICROBATCHES[config], LR, seed or 1)
     device = torch.device("cuda", dims.local_rank)
     seq, vocab = cfg.model.max_seq_len, cfg.model.vocab_size
     host = _host_batches(torch, vocab, batch, seq, 4, seed + dims.data_rank)
@@ -388,9 +389,9 @@ def run_reference(args, config: str) -> dict:
         return step.train_step(model, host[i % len(host)], optimizer)["train/ce_loss"].value
 
     # With expert parallelism the reference builds its permutation with one host-side tensor write per
-    # row (src/model/torch_backend.py:111-124): seconds per step.  Three warm-up and at most four timed
+    # row (src/model/torch_backend.py:111-124): seconds per step.  Three warm-up and at most two timed
     # steps keep its run within minutes.
-    n_warm, n_steps = (3, min(args.steps, 4)) if ep > 1 else (args.warmup, args.steps)
+    n_warm, n_steps = (3, min(args.steps, 2)) if ep > 1 else (args.warmup, args.steps)
     for i in range(n_warm):
         api_step(i)
     sampler = ClockSampler(device.index or 0)
@@ -418,7 +419,7 @@ def run_reference(args, config: str) -> dict:
     if cfg.model.num_experts > 1:
         ffn = next(b.ffn for b in model.blocks if hasattr(b, "ffn"))
         result["layer_fwd_bwd_ms"] = _moe_layer_ms(torch, dist, ffn, list(ffn.parameters()), batch // MICROBATCHES[config],
-                                                   seq, cfg.model.d_model, flush, device, iters=4 if ep > 1 else 10)
+                                                   seq, cfg.model.d_model, flush, device, iters=2 if ep > 1 else 10)
     del model, step, optimizer
     gc.collect()
     torch.cuda.empty_cache()

@@ -111,7 +111,7 @@ class TrainerConfig(_Strict):
     device_id: NonNegativeInt
     eval_every_step: int
     per_device_batch_size: PositiveInt
-    seed: PositiveInt
+    seed: NonNegativeInt  # the reference insists on seed > 0 (src/config.py:121); 0 is a valid seed here
 
 
 class CheckpointConfig(_Strict):

@@ -1,14 +1,17 @@
 """Grid sweeps: ``python -m nanotitan_b200.sweep <sweep.toml> [--dry-run] [--log-level L]``.
 
-A sweep file names a base config and lists values per dotted key; every point of the
-cartesian product is validated, named ``<base>__<key>-<value>__...`` and launched as
-its own `torch.distributed.run` job (reference: scripts/sweep.py:18-146).  The launch
-uses dp*pp*ep processes (the reference forgets ep_size).
+A sweep file names a base config and lists values per dotted key
+(`"optim.lr" = [1e-3, 5e-4]`).  The runner works on the *flat* form of a config - a
+`{"optim.lr": 0.001, "model.dtype": "bfloat16", ...}` map obtained from the validated
+`AppConfig` - so that an override is a plain dict update, a grid point is the base map plus one
+choice per swept key, and the TOML of a run is written straight from the flat map.  Every point is
+validated again as an `AppConfig`, named ``<base>__<key>-<value>__...`` and launched as its own
+`torch.distributed.run` job with dp*pp*ep processes (the reference's runner, scripts/sweep.py:97-144,
+sizes the job without ep_size).
 """
 from __future__ import annotations
 
 import argparse
-import copy
 import itertools
 import json
 import re
@@ -16,118 +19,123 @@ import subprocess
 import sys
 import tempfile
 import tomllib
+from collections.abc import Iterator
 from pathlib import Path
 from typing import Any
 
 from nanotitan_b200.config import AppConfig
 
-_BARE_KEY = re.compile(r"[A-Za-z0-9_-]+")
+Flat = dict[str, Any]
 
 
-def parse_args(argv=None) -> argparse.Namespace:
-    parser = argparse.ArgumentParser(description="Run a grid sweep described by TOML.")
-    parser.add_argument("sweep", type=Path, help="Path to the sweep TOML file.")
-    parser.add_argument("--dry-run", action="store_true", help="Validate and print every run only.")
-    parser.add_argument("--log-level", default="INFO", help="Logging level forwarded to the trainer.")
-    return parser.parse_args(argv)
+# ------------------------------------------------------------------ flat <-> nested
+def flatten(tree: dict[str, Any], prefix: str = "") -> Flat:
+    flat: Flat = {}
+    for key, value in tree.items():
+        path = f"{prefix}{key}"
+        if isinstance(value, dict):
+            flat.update(flatten(value, path + "."))
+        else:
+            flat[path] = value
+    return flat
 
 
-def load_toml(path: Path) -> dict[str, Any]:
-    with Path(path).open("rb") as fh:
-        return tomllib.load(fh)
+def unflatten(flat: Flat) -> dict[str, Any]:
+    tree: dict[str, Any] = {}
+    for path, value in flat.items():
+        *tables, leaf = path.split(".")
+        node = tree
+        for name in tables:
+            node = node.setdefault(name, {})
+        node[leaf] = value
+    return tree
 
 
-def set_dotted_value(config: dict[str, Any], dotted_key: str, value: Any) -> None:
-    *parents, leaf = dotted_key.split(".")
-    node = config
-    for part in parents:
-        node = node[part]
-    node[leaf] = value
+def _scalar(value: Any) -> str:
+    if isinstance(value, bool):
+        return "true" if value else "false"
+    if isinstance(value, (int, float)):
+        return repr(value)
+    if isinstance(value, (list, tuple)):
+        return "[" + ", ".join(_scalar(v) for v in value) + "]"
+    return json.dumps(str(value))
 
 
-def safe_fragment(value: Any) -> str:
+def dump_toml(config: dict[str, Any]) -> str:
+    """TOML text of a nested config of scalars: top-level keys first, then one `[table]` per
+    distinct key prefix in first-seen order."""
+    flat = flatten(config)
+    by_table: dict[str, list[str]] = {}
+    for path, value in flat.items():
+        if value is None:
+            continue  # TOML has no null; absent means "use the default"
+        table, _, leaf = path.rpartition(".")
+        by_table.setdefault(table, []).append(f"{leaf} = {_scalar(value)}")
+    chunks = ["\n".join(by_table.pop("", []))]
+    chunks += [f"[{table}]\n" + "\n".join(lines) for table, lines in by_table.items()]
+    return "\n\n".join(c for c in chunks if c) + "\n"
+
+
+# ------------------------------------------------------------------ grid
+def _slug(value: Any) -> str:
     text = str(value).lower() if isinstance(value, bool) else str(value)
     return re.sub(r"[^A-Za-z0-9_.-]+", "-", text).strip("-")
 
 
-def make_run_name(base_name: str, overrides: dict[str, Any]) -> str:
-    parts = [safe_fragment(base_name)]
-    parts += [f"{safe_fragment(k.replace('.', '-'))}-{safe_fragment(v)}" for k, v in overrides.items()]
-    return "__".join(parts)
+def grid_points(parameters: dict[str, list[Any]]) -> Iterator[Flat]:
+    keys = list(parameters)
+    for choice in itertools.product(*(parameters[k] for k in keys)):
+        yield dict(zip(keys, choice, strict=True))
 
 
-def _toml_value(value: Any) -> str:
-    if isinstance(value, bool):
-        return "true" if value else "false"
-    if isinstance(value, str):
-        return json.dumps(value)
-    return repr(value)
-
-
-def _toml_key(key: str) -> str:
-    return key if _BARE_KEY.fullmatch(key) else json.dumps(key)
-
-
-def dump_toml(config: dict[str, Any]) -> str:
-    """Minimal TOML writer for nested tables of scalars (enough for AppConfig dumps)."""
-    out: list[str] = []
-
-    def emit(table: dict[str, Any], path: tuple[str, ...]) -> None:
-        if path:
-            if out and out[-1] != "":
-                out.append("")
-            out.append("[" + ".".join(_toml_key(p) for p in path) + "]")
-        out.extend(f"{_toml_key(k)} = {_toml_value(v)}" for k, v in table.items() if not isinstance(v, dict))
-        for k, v in table.items():
-            if isinstance(v, dict):
-                emit(v, (*path, k))
-
-    emit(config, ())
-    return "\n".join(out) + "\n"
+def run_name(base: str, overrides: Flat) -> str:
+    return "__".join([_slug(base)] + [f"{_slug(k.replace('.', '-'))}-{_slug(v)}" for k, v in overrides.items()])
 
 
 def build_runs(sweep_path: Path) -> tuple[Path, list[tuple[str, dict[str, Any]]]]:
-    sweep = load_toml(sweep_path)
+    """-> (base config path, [(run name, nested config dict)]) for every grid point."""
+    with Path(sweep_path).open("rb") as fh:
+        sweep = tomllib.load(fh)
     base_path = Path(sweep["base_config"]).resolve()
-    base = AppConfig.model_validate(load_toml(base_path)).model_dump(mode="json")
-    keys = list(sweep["parameters"])
+    with base_path.open("rb") as fh:
+        base = flatten(AppConfig.model_validate(tomllib.load(fh)).model_dump(mode="json"))
     runs = []
-    for combo in itertools.product(*(sweep["parameters"][k] for k in keys)):
-        overrides = dict(zip(keys, combo, strict=True))
-        cfg = copy.deepcopy(base)
-        for key, value in overrides.items():
-            set_dotted_value(cfg, key, value)
-        cfg["run_name"] = make_run_name(str(base["run_name"]), overrides)
-        AppConfig.model_validate(cfg)
-        runs.append((cfg["run_name"], cfg))
+    for overrides in grid_points(sweep["parameters"]):
+        unknown = [k for k in overrides if k not in base]
+        if unknown:
+            raise KeyError(f"sweep keys not in the config schema: {unknown}")
+        point = {**base, **overrides, "run_name": run_name(str(base["run_name"]), overrides)}
+        config = AppConfig.model_validate(unflatten(point)).model_dump(mode="json")
+        runs.append((config["run_name"], config))
     return base_path, runs
 
 
+# ------------------------------------------------------------------ launch
 def launch_command(config: dict[str, Any], config_path: Path, log_level: str) -> list[str]:
-    rt = config["runtime"]
-    world = rt["dp_size"] * rt["pp_size"] * rt.get("ep_size", 1)
-    return [
-        sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
-        f"--nproc-per-node={world}", "-m", "nanotitan_b200.train", f"@{config_path}",
-        f"--log.level={log_level}",
-    ]
+    runtime = config["runtime"]
+    ranks = runtime["dp_size"] * runtime["pp_size"] * runtime.get("ep_size", 1)
+    return [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
+            f"--nproc-per-node={ranks}", "-m", "nanotitan_b200.train", f"@{config_path}", f"--log.level={log_level}"]
 
 
 def main(argv=None) -> int:
-    args = parse_args(argv)
-    sweep_path = args.sweep.resolve()
-    base_path, runs = build_runs(sweep_path)
-    print(f"Loaded {len(runs)} run(s) from {sweep_path} using {base_path}")
-    with tempfile.TemporaryDirectory(prefix="nanotitan-sweep-") as tmp:
-        for i, (name, config) in enumerate(runs, start=1):
-            cfg_path = Path(tmp) / f"run-{i:04d}.toml"
-            cfg_path.write_text(dump_toml(config), encoding="utf-8")
-            cmd = launch_command(config, cfg_path, args.log_level)
-            print(f"[{i}/{len(runs)}] {name}")
+    parser = argparse.ArgumentParser(description="Run every point of a grid sweep described by a TOML file.")
+    parser.add_argument("sweep", type=Path, help="sweep TOML: base_config + [parameters]")
+    parser.add_argument("--dry-run", action="store_true", help="validate and print the launch commands only")
+    parser.add_argument("--log-level", default="INFO", help="logging level passed to the trainer")
+    args = parser.parse_args(argv)
+    base_path, runs = build_runs(args.sweep.resolve())
+    print(f"{len(runs)} run(s) from {args.sweep} over {base_path}")
+    with tempfile.TemporaryDirectory(prefix="nt-sweep-") as scratch:
+        for number, (name, config) in enumerate(runs, start=1):
+            toml_path = Path(scratch) / f"{number:04d}-{name[:80]}.toml"
+            toml_path.write_text(dump_toml(config), encoding="utf-8")
+            command = launch_command(config, toml_path, args.log_level)
+            print(f"[{number}/{len(runs)}] {name}")
             if args.dry_run:
-                print("  " + subprocess.list2cmdline(cmd))
-                continue
-            subprocess.run(cmd, check=True)
+                print("    " + subprocess.list2cmdline(command))
+            else:
+                subprocess.run(command, check=True)
     return 0
 
 

@@ -1,62 +1,78 @@
-"""Small helpers shared by the entrypoints (reference: src/utils.py)."""
+"""Helpers shared by the entrypoints: logging, seeding, dtype names, config arguments.
+
+The names are the reference's (src/utils.py:13-57): `setup_logging`, `normalize_config_arg`,
+`load_run_config`, `seed_everything`, `reduce_scalars`, `resolve_dtype`.  Helpers the reference
+defines but never calls live only in the `src.utils` compatibility module.
+"""
 from __future__ import annotations
 
 import logging
+import os
 import random
-from datetime import datetime
-from pathlib import Path
 
 import torch
 import torch.distributed as dist
 
 from nanotitan_b200.config import AppConfig, load_config
 
+__all__ = ["setup_logging", "normalize_config_arg", "load_run_config", "seed_everything", "reduce_scalars",
+           "resolve_dtype", "DTYPE_NAMES"]
+
+# accepted spellings of the three training dtypes (the TOML files use the torch names)
+DTYPE_NAMES = {
+    "float32": torch.float32, "fp32": torch.float32, "float": torch.float32,
+    "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+    "float16": torch.float16, "fp16": torch.float16, "half": torch.float16,
+    "float64": torch.float64, "fp64": torch.float64, "double": torch.float64,
+}
+
+
+def resolve_dtype(dtype):
+    """Config spelling -> `torch.dtype`.  Dtypes and None pass through; an unknown name is an error
+    here, at start-up, not at the first tensor creation."""
+    if dtype is None or isinstance(dtype, torch.dtype):
+        return dtype
+    try:
+        return DTYPE_NAMES[str(dtype).lower()]
+    except KeyError:
+        raise ValueError(f"unknown dtype {dtype!r}; known: {sorted(DTYPE_NAMES)}") from None
+
 
 def setup_logging(level: str = "INFO") -> None:
-    logging.basicConfig(
-        level=getattr(logging, str(level).upper(), logging.INFO),
-        format="%(asctime)s | %(levelname)s | %(name)s | %(message)s",
-    )
-
-
-def setup_tensorboard(run_name: str, log_root: str = "runs"):
-    from nanotitan_b200.metrics import MetricsLogger
-
-    stamp = datetime.now().strftime("%Y%m%d-%H%M%S")
-    return MetricsLogger(f"{run_name}-{stamp}", log_root=log_root)
+    """Root logger at `level` (a name such as "debug" or a number), each line tagged with the rank
+    the launcher gave this process."""
+    numeric = logging.getLevelName(str(level).upper())
+    if not isinstance(numeric, int):
+        numeric = int(level) if str(level).isdigit() else logging.INFO
+    rank = os.environ.get("RANK")
+    tag = f"rank {rank} | " if rank is not None else ""
+    logging.basicConfig(level=numeric, format=f"%(asctime)s | {tag}%(levelname)s | %(name)s | %(message)s")
 
 
 def normalize_config_arg(config_arg: str) -> str:
-    """Launcher style allows ``@path.toml``; strip the marker."""
-    return config_arg[1:] if config_arg.startswith("@") else config_arg
+    """`@configs/x.toml` (launcher style) and `configs/x.toml` name the same file."""
+    return config_arg.removeprefix("@")
 
 
 def load_run_config(config_arg: str) -> AppConfig:
     return load_config(normalize_config_arg(config_arg))
 
 
-def resolve_device(device_id: int) -> torch.device:
-    return torch.device(f"cuda:{device_id}") if torch.cuda.is_available() else torch.device("cpu")
-
-
 def seed_everything(seed: int) -> None:
+    """Same seed on every rank: replicas build identical initial weights before the first
+    broadcast, as in the reference (src/train.py:94)."""
     random.seed(seed)
-    torch.manual_seed(seed)
-    if torch.cuda.is_available():
-        torch.cuda.manual_seed_all(seed)
+    torch.manual_seed(seed)  # seeds the CPU generator and every CUDA device's
+    try:
+        import numpy as np
+
+        np.random.seed(seed % (1 << 32))
+    except ImportError:
+        pass
 
 
-def reduce_scalars(scalar_tensor: torch.Tensor, pp_group) -> None:
+def reduce_scalars(values: torch.Tensor, group) -> None:
+    """In-place SUM over `group` (parameter counts over the pipeline stages); a no-op without a
+    process group."""
     if dist.is_available() and dist.is_initialized():
-        dist.all_reduce(scalar_tensor, op=dist.ReduceOp.SUM, group=pp_group)
-
-
-def resolve_dtype(dtype):
-    """'bfloat16' -> torch.bfloat16; torch dtypes and None pass through."""
-    if dtype is None or isinstance(dtype, torch.dtype):
-        return dtype
-    return getattr(torch, dtype)
-
-
-def get_profiler_trace_dir(run_name: str, log_root: str = "runs") -> Path:
-    return Path(log_root) / run_name / "profiler"
+        dist.all_reduce(values, op=dist.ReduceOp.SUM, group=group)
