@@ -252,6 +252,7 @@ def run_ours(args, config: str) -> dict:
     from nanotitan_b200.train import build_training
     from nanotitan_b200.utils import seed_everything
 
+    os.environ.setdefault("NT_STRICT", "1")  # an op that would leave this library's kernels raises instead
     dp, pp, ep, par = _parallelism(config, args.gpus)
     model_kw = dict(MODELS[config], moe_backend="cuda")
     batch, seed = BATCH[config], SEEDS[config]
@@ -290,16 +291,23 @@ def run_ours(args, config: str) -> dict:
     # step's before the timed region closes.
     in_flight = []
 
+    recv_wait = []  # per step: compute-stream idle seconds across the waits for pipeline-boundary tensors
+
+    def _collect(pending):
+        metrics = pending.result()
+        recv_wait.append(metrics["time/pp_recv_wait"].value)
+        return metrics["train/ce_loss"].value
+
     def api_step(i):
         in_flight.append(step.train_step(model, host[i % len(host)], optimizer, collect_metrics="deferred"))
         if len(in_flight) > 1:
-            return in_flight.pop(0).result()["train/ce_loss"].value
+            return _collect(in_flight.pop(0))
         return None
 
     def api_finish():
         loss = None
         while in_flight:
-            loss = in_flight.pop(0).result()["train/ce_loss"].value
+            loss = _collect(in_flight.pop(0))
         return loss
 
     for i in range(max(args.warmup, 3)):  # two ordinary steps, then the step that captures the CUDA graph
@@ -351,6 +359,12 @@ def run_ours(args, config: str) -> dict:
         "paths": _paths(model, reducers, dims),
         "replicas_identical": _replicas_identical(torch, dist, reducers) if args.gpus > 1 else None,
     }
+    if pp > 1:
+        # stage idle time waiting for boundary tensors, mean over the timed end-to-end steps, max over ranks
+        w = torch.tensor([sum(recv_wait[-args.steps:]) / max(1, args.steps) * 1e3], device=device, dtype=torch.float64)
+        dist.all_reduce(w, op=dist.ReduceOp.MAX)
+        result["pp_recv_wait_ms_per_step"] = w.item()
+        result["pp_prepost"] = os.environ.get("NT_PP_PREPOST", "1") != "0"
     if cfg.model.num_experts > 1:
         ffn = next(b.ffn for b in model.blocks if hasattr(b, "ffn"))
         result["layer_fwd_bwd_ms"] = _moe_layer_ms(torch, dist, ffn, list(ffn.parameters()), batch // MICROBATCHES[config],

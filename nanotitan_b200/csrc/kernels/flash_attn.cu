@@ -17,9 +17,17 @@
 // Splitting backward into a dQ pass and a dK/dV pass recomputes the scores once more but needs
 // no atomics, so gradients are bit-reproducible.
 //
-// Warp roles: warp 0 TMA producer, warp 1 MMA issuer (+ TMEM owner), warps 2-5 softmax/epilogue.
-// TMEM use is <= 256 columns and shared memory ~100 KB so two CTAs share an SM and overlap
-// each other's MMA and exponential phases.  Every mbarrier wait is bounded (see sm100.cuh).
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer (+ TMEM owner), warps 2-9 softmax/epilogue:
+// two warpgroups of 128 threads.  Thread i of either warpgroup owns row i of the resident tile
+// (a warp reads the TMEM lanes of its quarter, warp % 4), and the two warpgroups split the 64
+// streamed columns of a step: warpgroup g works on columns [32 g, 32 g + 32).  In backward the
+// halves are independent.  In forward the row maximum is exchanged through shared memory (one
+// named barrier per step), each warpgroup keeps its own partial row sum and folds its own half of
+// the head dimension of the P.V product; the partial sums meet once, at the end.
+// TMEM use is <= 256 columns and shared memory ~100 KB so two CTAs share an SM: 16 softmax warps
+// per SM hide the tcgen05.ld and exponential latencies of one another.  Every mbarrier wait is
+// bounded (see sm100.cuh); after an abandoned wait a thread keeps walking the loop so that the
+// named barriers still see every thread.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <ATen/ATen.h>
@@ -37,7 +45,8 @@ namespace attn {
 
 enum Mode : int { kFwd = 0, kDq = 1, kDkv = 2 };
 constexpr int BR = 128;  // resident rows
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;
+constexpr int SOFTMAX_THREADS = 256;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct Args {
@@ -59,14 +68,15 @@ struct Cfg {
   static constexpr int R_TILE = BR * DH * 2;                     // bytes
   static constexpr int C_TILE = BC * DH * 2;
   static constexpr int N_R = MODE == kFwd ? 1 : 2;
-  static constexpr int STAGES = 2;
+  // operand stages of the streamed tiles; dK/dV at head dim 64 keeps two so that two CTAs still fit an SM's shared memory
+  static constexpr int STAGES = (MODE == kDkv && DH == 64) ? 2 : 3;
   static constexpr int E_TILE = BR * BC * 2;
   static constexpr int N_E = MODE == kDkv ? 2 : 1;
   static constexpr int OFF_R = 0;
   static constexpr int OFF_C = OFF_R + N_R * R_TILE;
   static constexpr int OFF_E = OFF_C + STAGES * 2 * C_TILE;
-  static constexpr int OFF_VEC = OFF_E + N_E * E_TILE;           // dkv: lse / dsum of the streamed queries
-  static constexpr int OFF_BAR = OFF_VEC + (MODE == kDkv ? STAGES * 2 * BC * 4 : 0);
+  static constexpr int OFF_VEC = OFF_E + N_E * E_TILE;           // dkv: lse / dsum of the streamed queries; fwd: row max / sum exchange
+  static constexpr int OFF_BAR = OFF_VEC + 4096;
   static constexpr int TOTAL = OFF_BAR + 16 * 8 + 16 + 1024;
   static constexpr uint32_t TMEM_COLS = 256;
   // forward double-buffers T1 (columns 0 and 64); backward keeps T1 at 0 and T2 at 64
@@ -86,7 +96,18 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo, uint3
   return d;
 }
 
-__device__ __forceinline__ void named_sync_softmax() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void named_sync_softmax() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// 32 lanes x 16 consecutive fp32 columns (thread i of the warp receives lane base_lane + i)
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 
 __device__ __forceinline__ uint32_t pack_pair(float lo, float hi, int dtype) {
   if (dtype == 1) {
@@ -97,13 +118,14 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi, int dtype) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Write 32 consecutive values of row `r` (columns c0 .. c0+31 of a 128 x BC tile) into a K-major,
+// Write N (16 or 32) consecutive values of row `r` (columns c0 .. c0+N-1 of a 128 x BC tile) into a K-major,
 // 128-byte-swizzled operand tile made of 64-column chunks of [128 rows][128 B].
-__device__ __forceinline__ void write_e_chunk(uint8_t* tile, int r, int c0, const float (&v)[32], int dtype) {
+template <int N>
+__device__ __forceinline__ void write_e_chunk(uint8_t* tile, int r, int c0, const float (&v)[N], int dtype) {
   uint8_t* row = tile + (c0 >> 6) * (BR * 128) + r * 128;
   const int u0 = (c0 & 63) >> 3;
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
+  for (int u = 0; u < N / 8; ++u) {
     uint4 q;
     q.x = pack_pair(v[8 * u + 0], v[8 * u + 1], dtype);
     q.y = pack_pair(v[8 * u + 2], v[8 * u + 3], dtype);
@@ -142,13 +164,13 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint64_t* r_full = bars;            // 1
-  uint64_t* c_full = bars + 1;        // 2
-  uint64_t* c_empty = bars + 3;       // 2
-  uint64_t* t_full = bars + 5;        // 1 (forward: buffer 0)
-  uint64_t* t_full_b = bars + 9;      // forward: buffer 1
-  uint64_t* e_full = bars + 6;        // 1 (128 arrivals)
-  uint64_t* e_empty = bars + 7;       // 1
-  uint64_t* acc_full = bars + 8;      // 1
+  uint64_t* c_full = bars + 1;        // STAGES (<= 4)
+  uint64_t* c_empty = bars + 5;       // STAGES (<= 4)
+  uint64_t* t_full = bars + 9;        // 1 (forward: score buffer 0)
+  uint64_t* t_full_b = bars + 10;     // forward: score buffer 1
+  uint64_t* e_full = bars + 11;       // 1 (one arrival per softmax warp)
+  uint64_t* e_empty = bars + 12;      // 1
+  uint64_t* acc_full = bars + 13;     // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -173,10 +195,10 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(r_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&c_full[s], 1); mbar_init(&c_empty[s], 1); }
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&c_full[s], 1); mbar_init(&c_empty[s], 1); }
     mbar_init(t_full, 1);
     mbar_init(t_full_b, 1);
-    mbar_init(e_full, 4);  // one arrival per softmax warp
+    mbar_init(e_full, SOFTMAX_THREADS / 32);  // one arrival per softmax warp
     mbar_init(e_empty, 1);
     mbar_init(acc_full, 1);
     *abort_flag = 0u;
@@ -223,16 +245,16 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
       // Forward keeps two score buffers in TMEM: the scores of step it+1 are issued before the
       // softmax threads have finished step it, so they never wait for the tensor core.
       auto issue_scores = [&](int it) -> bool {
-        const int st = it & 1;
-        if (!mbar_wait(&c_full[st], (it >> 1) & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 210 + st)) return false;
+        const int st = it % C::STAGES, tb = it & 1;  // operand stage, score buffer
+        if (!mbar_wait(&c_full[st], (it / C::STAGES) & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 210 + st)) return false;
         tc_fence_after();
         if (lane == 0) {
           const uint32_t ca = smem_u32(smem + C::OFF_C + st * 2 * C::C_TILE);
 #pragma unroll
           for (int ks = 0; ks < DH / 16; ++ks)
-            umma_f16(tmem_base + C::COL_T1 + st * BC, make_desc(ra + ks * 32, 16, C::SBO_RC, C::SWZ),
+            umma_f16(tmem_base + C::COL_T1 + tb * BC, make_desc(ra + ks * 32, 16, C::SBO_RC, C::SWZ),
                      make_desc(ca + ks * 32, 16, C::SBO_RC, C::SWZ), idesc_t, ks != 0);
-          umma_commit(st ? t_full_b : t_full);
+          umma_commit(tb ? t_full_b : t_full);
         }
         __syncwarp();
         return true;
@@ -243,7 +265,7 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
         if (!mbar_wait(e_full, it & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 220)) { ok = false; break; }
         tc_fence_after();
         if (lane == 0) {
-          const int st = it & 1;
+          const int st = it % C::STAGES;
           const uint32_t cb = smem_u32(smem + C::OFF_C + st * 2 * C::C_TILE) + C::C_TILE;  // V
 #pragma unroll
           for (int ks = 0; ks < BC / 16; ++ks)
@@ -305,21 +327,24 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
       if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
     }
   } else {
-    // ------------------------------------------------------------------ softmax / epilogue (128 threads)
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;  // row of the resident tile owned by this thread
+    // ------------------------------------------------------------------ softmax / epilogue (2 x 128 threads)
+    const int quarter = warp & 3;           // TMEM lane quarter this warp may read
+    const int wg = (warp - 2) >> 2;         // warpgroup: which 32 of the 64 streamed columns
+    const int r = quarter * 32 + lane;      // row of the resident tile owned by this thread
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const int row_idx = r0 + r;         // query index (fwd/dq) or key index (dkv)
+    const int row_idx = r0 + r;             // query index (fwd/dq) or key index (dkv)
     const float sl2 = args.scale * LOG2E;
     uint8_t* e1 = smem + C::OFF_E;
     uint8_t* e2 = e1 + C::E_TILE;
     float* vec = reinterpret_cast<float*>(smem + C::OFF_VEC);
     const long long bh = static_cast<long long>(b) * args.H + h;
+    constexpr int HD = DH / 2;              // head-dim columns each warpgroup folds / stores
+    const int col_half = wg * HD;
 
     float m_run = -INFINITY, l_run = 0.f;
-    float o_acc[DH];
+    float o_acc[HD];
 #pragma unroll
-    for (int i = 0; i < DH; ++i) o_acc[i] = 0.f;
+    for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
     float my_lse = 0.f, my_dsum = 0.f;
     if (MODE == kDq && row_idx < S) {
       my_lse = args.lse[bh * S + row_idx] * LOG2E;
@@ -328,58 +353,61 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
     bool ok = true;
     if (MODE == kFwd) {
       float alpha_prev = 0.f;
-      // fold the P.V product of step `it` (already rescaled relative to that step's row max)
+      float* mx = vec;  // [2 (step parity)][2 (warpgroup)][128]: the warpgroups' row maxima of a step
+      // fold this warpgroup's half of the P.V product of step `it` (already scaled to that step's row max)
       auto fold_pv = [&](int it) -> bool {
         if (!mbar_wait(acc_full, it & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 320)) return false;
         tc_fence_after();
 #pragma unroll
-        for (int cc = 0; cc < DH; cc += 32) {
-          uint32_t t[32];
-          tmem_ld_32x32(lane_addr + C::COL_ACC1 + cc, t);
+        for (int cc = 0; cc < HD; cc += 16) {
+          uint32_t t[16];
+          tmem_ld_32x16(lane_addr + C::COL_ACC1 + col_half + cc, t);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o_acc[cc + i] = o_acc[cc + i] * alpha_prev + __uint_as_float(t[i]);
+          for (int i = 0; i < 16; ++i) o_acc[cc + i] = o_acc[cc + i] * alpha_prev + __uint_as_float(t[i]);
         }
         tc_fence_before();
         return true;
       };
-      for (int it = 0; it < n_iter && ok; ++it) {
-        const int c0 = it * BC;
-        if (!mbar_wait((it & 1) ? t_full_b : t_full, (it >> 1) & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 300)) { ok = false; break; }
-        tc_fence_after();
-        uint32_t t[BC];
-        {
-          uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&t[0]);
-          uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&t[32]);
-          tmem_ld_32x32(lane_addr + C::COL_T1 + (it & 1) * BC, lo);
-          tmem_ld_32x32(lane_addr + C::COL_T1 + (it & 1) * BC + 32, hi);
+      for (int it = 0; it < n_iter; ++it) {  // runs to the end even after an abandoned wait: the named barrier needs every thread
+        const int c0 = it * BC + wg * 32;  // first key of this warpgroup's half
+        bool step_ok = ok;
+        if (step_ok) step_ok = mbar_wait((it & 1) ? t_full_b : t_full, (it >> 1) & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 300);
+        uint32_t t[32];
+        float m_loc = -INFINITY;
+        if (step_ok) {
+          tc_fence_after();
+          tmem_ld_32x32(lane_addr + C::COL_T1 + (it & 1) * BC + wg * 32, t);
           tmem_ld_wait();
-        }
-        tc_fence_before();
-        // tiles left of the diagonal and inside the sequence need no mask (uniform over the CTA)
-        const bool need_mask = (c0 + BC - 1 > r0) || (c0 + BC > S);
-        float m_new = m_run;
-        if (need_mask) {
+          tc_fence_before();
+          // tiles left of the diagonal and inside the sequence need no mask (uniform over the warpgroup)
+          const bool need_mask = (c0 + 31 > r0) || (c0 + 32 > S);
+          if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < BC; ++i) {
-            const int key = c0 + i;
-            if (!(key <= row_idx && key < S)) t[i] = 0xff800000u;  // -inf
-            m_new = fmaxf(m_new, __uint_as_float(t[i]));
+            for (int i = 0; i < 32; ++i) {
+              const int key = c0 + i;
+              if (!(key <= row_idx && key < S)) t[i] = 0xff800000u;  // -inf
+            }
           }
-        } else {
-          float m4[4] = {m_new, m_new, m_new, m_new};  // four independent chains instead of one of 64
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four independent chains
 #pragma unroll
-          for (int i = 0; i < BC; i += 4) {
+          for (int i = 0; i < 32; i += 4) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) m4[j] = fmaxf(m4[j], __uint_as_float(t[i + j]));
           }
-          m_new = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+          m_loc = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         }
+        float* mx_it = mx + (it & 1) * 2 * BR;
+        mx_it[wg * BR + r] = m_loc;
+        named_sync_softmax();
+        const float m_other = mx_it[(1 - wg) * BR + r];
+        if (!step_ok) { ok = false; continue; }
+        const float m_new = fmaxf(m_run, fmaxf(m_loc, m_other));
         const float alpha = exp2f((m_run - m_new) * sl2);  // first tile: m_run = -inf -> 0
         const float shift = m_new * sl2;
         float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < BC; i += 4) {
+        for (int i = 0; i < 32; i += 4) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float pi = exp2f(fmaf(__uint_as_float(t[i + j]), sl2, -shift));  // exp2(-inf) = 0 for masked entries
@@ -389,12 +417,10 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
         }
         const float l_add = (l4[0] + l4[1]) + (l4[2] + l4[3]);
         // the previous step's P.V finished long ago; folding it here keeps its latency off the loop
-        if (it > 0 && !fold_pv(it - 1)) { ok = false; break; }
+        if (it > 0 && !fold_pv(it - 1)) { ok = false; continue; }
         {
-          float (&plo)[32] = *reinterpret_cast<float (*)[32]>(&t[0]);
-          float (&phi)[32] = *reinterpret_cast<float (*)[32]>(&t[32]);
-          write_e_chunk(e1, r, 0, plo, DT);
-          write_e_chunk(e1, r, 32, phi, DT);
+          float (&pr)[32] = *reinterpret_cast<float (*)[32]>(&t[0]);
+          write_e_chunk<32>(e1, r, wg * 32, pr, DT);
         }
         fence_proxy_async_smem();
         __syncwarp();
@@ -404,14 +430,19 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
         alpha_prev = alpha;
       }
       if (ok && n_iter > 0) ok = fold_pv(n_iter - 1);
+      // the two partial row sums meet (both were kept relative to the same running maximum)
+      float* ls = vec + 4 * BR;
+      ls[wg * BR + r] = l_run;
+      named_sync_softmax();
+      l_run += ls[(1 - wg) * BR + r];
     }
     int stage = 0;
     for (int it = 0; it < n_iter && MODE != kFwd; ++it) {  // runs to the end even after an abandoned wait: see named_sync below
-      const int c0 = (c_begin + it) * BC;  // first streamed index (key for fwd/dq, query for dkv)
+      const int c0 = (c_begin + it) * BC;  // first streamed index (key for dq, query for dkv)
       if (MODE == kDkv) {
         // stage the streamed queries' lse / dsum in shared memory (values past S are neutral)
         float* vl = vec + stage * 2 * BC;
-        if (r < BC) {
+        if (wg == 0 && r < BC) {
           const int qi = c0 + r;
           vl[r] = qi < S ? args.lse[bh * S + qi] * LOG2E : 0.f;
           vl[BC + r] = qi < S ? args.dsum[bh * S + qi] : 0.f;
@@ -419,26 +450,28 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
         named_sync_softmax();
       }
       if (!ok) { if (++stage == C::STAGES) stage = 0; continue; }
-      if (!mbar_wait(t_full, it & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 300)) { ok = false; continue; }
+      if (!mbar_wait(t_full, it & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 300)) { ok = false; if (++stage == C::STAGES) stage = 0; continue; }
       tc_fence_after();
       if (it > 0) {
-        if (!mbar_wait(e_empty, (it - 1) & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 310)) { ok = false; continue; }
+        if (!mbar_wait(e_empty, (it - 1) & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 310)) { ok = false; if (++stage == C::STAGES) stage = 0; continue; }
       }
       {
         const float* vl = vec + stage * 2 * BC;
+        const int cw = wg * 32;  // this warpgroup's 32 columns of the step
         // only tiles that straddle the diagonal or the end of the sequence need the mask (uniform)
-        const bool need_mask = (MODE == kDq) ? ((c0 + BC - 1 > r0) || (c0 + BC > S)) : ((r0 + BR - 1 > c0) || (c0 + BC > S));
+        const bool need_mask = (MODE == kDq) ? ((c0 + cw + 31 > r0) || (c0 + cw + 32 > S)) : ((r0 + BR - 1 > c0 + cw) || (c0 + cw + 32 > S));
         auto process = [&](auto mask_tag) {
           constexpr bool MASK = decltype(mask_tag)::value;
-#pragma unroll 1
-          for (int cc = 0; cc < BC; cc += 32) {
-            uint32_t t1[32], t2[32];
-            tmem_ld_32x32(lane_addr + C::COL_T1 + cc, t1);
-            tmem_ld_32x32(lane_addr + C::COL_T2 + cc, t2);
-            tmem_ld_wait();
-            float pv[32], ds[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
+          for (int sub = 0; sub < 32; sub += 16) {
+            const int cc = cw + sub;
+            uint32_t t1[16], t2[16];
+            tmem_ld_32x16(lane_addr + C::COL_T1 + cc, t1);
+            tmem_ld_32x16(lane_addr + C::COL_T2 + cc, t2);
+            tmem_ld_wait();
+            float pv[16], ds[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
               const int ci = c0 + cc + i;
               bool keep = true;
               float lse2, dsum;
@@ -456,10 +489,10 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
               ds[i] = p * (__uint_as_float(t2[i]) - dsum) * args.scale;
             }
             if (MODE == kDq) {
-              write_e_chunk(e1, r, cc, ds, DT);
+              write_e_chunk<16>(e1, r, cc, ds, DT);
             } else {
-              write_e_chunk(e1, r, cc, pv, DT);
-              write_e_chunk(e2, r, cc, ds, DT);
+              write_e_chunk<16>(e1, r, cc, pv, DT);
+              write_e_chunk<16>(e2, r, cc, ds, DT);
             }
           }
         };
@@ -477,40 +510,36 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
     if (ok && MODE != kFwd && n_iter > 0) ok = mbar_wait(acc_full, 0, abort_flag, args.status, kKernelAttnFwd + MODE, 330);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
-    if (ok && n_iter > 0 && row_idx < S) {
-      const long long off = static_cast<long long>(b) * args.o_sb + static_cast<long long>(row_idx) * args.o_ss +
-                            static_cast<long long>(h) * args.o_sh;
-      if (MODE == kFwd) {
+    const long long out_off = static_cast<long long>(b) * args.o_sb + static_cast<long long>(row_idx) * args.o_ss +
+                              static_cast<long long>(h) * args.o_sh + col_half;
+    if (MODE == kFwd) {
+      if (ok && n_iter > 0 && row_idx < S) {
         const float inv = 1.f / l_run;
 #pragma unroll
-        for (int i = 0; i < DH; ++i) o_acc[i] *= inv;
-        store_row<DH>(args.out0, off, o_acc, DT);
-        args.lse[bh * S + row_idx] = m_run * args.scale + logf(l_run);
+        for (int i = 0; i < HD; ++i) o_acc[i] *= inv;
+        store_row<HD>(args.out0, out_off, o_acc, DT);
+        if (wg == 0) args.lse[bh * S + row_idx] = m_run * args.scale + logf(l_run);
       }
-    }
-    if (MODE != kFwd) {
-      // all 32 lanes of a warp take part in tcgen05.ld; rows past S are read but not stored
+    } else {
+      // all 32 lanes of a warp take part in tcgen05.ld; rows past S are read but not stored.
+      // Each warpgroup stores its half of the head dimension of every output.
 #pragma unroll
       for (int which = 0; which < (MODE == kDkv ? 2 : 1); ++which) {
-        float v[DH];
+        float v[HD];
         if (ok && n_iter > 0) {
 #pragma unroll
-          for (int cc = 0; cc < DH; cc += 32) {
-            uint32_t t[32];
-            tmem_ld_32x32(lane_addr + (which == 0 ? C::COL_ACC1 : C::COL_ACC2) + cc, t);
+          for (int cc = 0; cc < HD; cc += 16) {
+            uint32_t t[16];
+            tmem_ld_32x16(lane_addr + (which == 0 ? C::COL_ACC1 : C::COL_ACC2) + col_half + cc, t);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[cc + i] = __uint_as_float(t[i]);
+            for (int i = 0; i < 16; ++i) v[cc + i] = __uint_as_float(t[i]);
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < DH; ++i) v[i] = 0.f;
+          for (int i = 0; i < HD; ++i) v[i] = 0.f;
         }
-        if (ok && row_idx < S) {
-          const long long off = static_cast<long long>(b) * args.o_sb + static_cast<long long>(row_idx) * args.o_ss +
-                                static_cast<long long>(h) * args.o_sh;
-          store_row<DH>(which == 0 ? args.out0 : args.out1, off, v, DT);
-        }
+        if (ok && row_idx < S) store_row<HD>(which == 0 ? args.out0 : args.out1, out_off, v, DT);
       }
     }
     tc_fence_before();

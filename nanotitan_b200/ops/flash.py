@@ -12,7 +12,7 @@ def supported(q, k, v) -> bool:
         return False
     return (
         q.dtype in (torch.bfloat16, torch.float16)
-        and q.shape[-1] in (32, 64, 128)
+        and q.shape[-1] in (32, 64)
         and q.shape == k.shape == v.shape
     )
 

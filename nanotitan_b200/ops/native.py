@@ -6,11 +6,30 @@ cuBLAS through torch, which only happens off the benchmarked path.
 """
 from __future__ import annotations
 
+import logging
 import math
+import os
 
 import torch
 
 from nanotitan_b200.ops.ext import get_ext
+
+logger = logging.getLogger(__name__)
+_FALLBACKS_SEEN: set = set()
+
+
+def library_fallback(op: str, why: str) -> None:
+    """Called whenever a GPU op leaves this library's kernels for a PyTorch / cuBLAS / cuDNN one
+    (operands the tcgen05 kernels cannot take: fp32, rows that are not 16-byte multiples, head sizes
+    other than 32 / 64).  Never silent: logged once per (op, reason) at WARNING, and an error when
+    `NT_STRICT=1` - benchmarks and the multi-GPU tests run with the native kernels only."""
+    if os.environ.get("NT_STRICT", "0") == "1":
+        raise RuntimeError(f"{op}: would fall back to a library kernel ({why}) and NT_STRICT=1 forbids it")
+    key = (op, why)
+    if key not in _FALLBACKS_SEEN:
+        _FALLBACKS_SEEN.add(key)
+        logger.warning("%s runs on a library kernel, not on nanotitan_cuda: %s", op, why)
+
 
 DENSE, GROUPED_M, GROUPED_K = 0, 1, 2
 B_ONE, B_SPLIT_N, B_SPLIT_K, B_DUAL = 0, 1, 2, 3
@@ -136,6 +155,7 @@ def qkv_attention(x, wq, wk, wv, heads, d_head, scale):
     if fused:
         qkv = _QKVProjection.apply(x, wq, wk, wv)
         return flash.flash_attention_qkv(qkv, heads, d_head, scale).reshape(*x.shape[:-1], inner)
+    library_fallback("qkv_attention", f"dtype {x.dtype}, head dim {d_head}, inner width {inner}: needs bf16/fp16, head dim 32 or 64")
     b, s, _ = x.shape
     q, k, v = (linear(x, w).view(b, s, heads, d_head) for w in (wq, wk, wv))
     return causal_attention(q, k, v, scale).reshape(b, s, inner)
@@ -144,6 +164,7 @@ def qkv_attention(x, wq, wk, wv, heads, d_head, scale):
 def linear(x, w, residual=None):
     if tc_ok(x.reshape(-1, x.shape[-1]), w) and w.dim() == 2:
         return _Linear.apply(x, w, residual)
+    library_fallback("linear", f"operands {tuple(x.shape)} {x.dtype} x {tuple(w.shape)} {w.dtype} are not TMA-addressable 16-bit matrices")
     y = x @ w
     return y if residual is None else y + residual
 
@@ -272,6 +293,7 @@ def linear_cross_entropy(x, w_unembed, targets):
     x2 = _rows(x)
     if tc_ok(x2, w_unembed):
         return _LinearCrossEntropy.apply(x2, w_unembed, targets.reshape(-1))
+    library_fallback("linear_cross_entropy", f"operands {tuple(x2.shape)} {x2.dtype} x {tuple(w_unembed.shape)} are not TMA-addressable 16-bit matrices")
     return cross_entropy(x2 @ w_unembed.t(), targets.reshape(-1))
 
 

@@ -71,6 +71,8 @@ class PendingMetrics:
     def __init__(self, owner, model, host_f, status, done, clock, host_start, n_mb, n_local):
         self.owner, self.model, self.host_f, self.status, self.done = owner, model, host_f, status, done
         self.clock, self.host_start, self.n_mb, self.n_local = clock, host_start, n_mb, n_local
+        self.recv_waits = list(owner._recv_waits)
+        self.recv_wait_s = 0.0
         self._metrics = None
 
     def result(self) -> dict:
@@ -112,6 +114,7 @@ class PipelineParallel:
         self._graph: _StepGraph | None = None
         self._eager_steps = 0
         self.graph_replays = 0
+        self._recv_waits: list = []
 
     # ------------------------------------------------------------------ helpers
     def synchronize_device(self) -> None:
@@ -146,12 +149,35 @@ class PipelineParallel:
         )
 
     def _post_recvs(self, src: int, count: int):
-        """Pre-post `count` receives from `src`; returns [(buffer, work)] in arrival order."""
+        """Pre-post `count` receives from `src`; returns [(buffer, work)] in arrival order.
+        With `NT_PP_PREPOST=0` nothing is posted ahead: `_recv` then posts each receive when its
+        microbatch needs it (the reference's blocking order, src/parallel/pp.py:58,183), which is
+        what the stage-idle metric `time/pp_recv_wait` is compared against."""
+        if os.environ.get("NT_PP_PREPOST", "1") == "0":
+            return [None] * count
         posted = []
         for _ in range(count):
             buf = self._boundary_buffer()
             posted.append((buf, dist.irecv(buf, src=src, group=self.dim.pp_group)))
         return posted
+
+    def _recv(self, posted, src: int) -> torch.Tensor:
+        """Wait for one boundary tensor.  The compute stream's idle time across the wait is recorded
+        between two events (`time/pp_recv_wait` sums them per step)."""
+        if posted is None:
+            buf = self._boundary_buffer()
+            posted = (buf, dist.irecv(buf, src=src, group=self.dim.pp_group))
+        buf, work = posted
+        timed = self.device.type == "cuda" and not torch.cuda.is_current_stream_capturing()
+        if timed:
+            before = torch.cuda.Event(enable_timing=True)
+            before.record()
+        work.wait()
+        if timed:
+            after = torch.cuda.Event(enable_timing=True)
+            after.record()
+            self._recv_waits.append((before, after))
+        return buf
 
     def _send(self, tensor: torch.Tensor, dst: int) -> None:
         self._pending.append((tensor, dist.isend(tensor.contiguous(), dst=dst, group=self.dim.pp_group)))
@@ -215,6 +241,7 @@ class PipelineParallel:
                 clock.mark(name)
 
         self._zero_grad(optimizer)
+        self._recv_waits = []
         ce_losses, aux_losses, stats_list = [], [], []
         with nvtx_range("forward_pass"):
             recvs = [] if first else self._post_recvs(self.dim.prev_pp_rank, n_mb)
@@ -222,8 +249,7 @@ class PipelineParallel:
                 if first:
                     mb_x = mb_x.to(self.device, non_blocking=True)
                 else:
-                    mb_x, work = recvs[i]
-                    work.wait()
+                    mb_x = self._recv(recvs[i], self.dim.prev_pp_rank)
                     mb_x.requires_grad_()
                     self.stage_inputs.append(mb_x)
                 if last:
@@ -378,6 +404,7 @@ class PipelineParallel:
     def _finish_metrics(self, pending: "PendingMetrics") -> dict:
         if pending.done is not None:
             pending.done.synchronize()  # this step only: later steps may already be running
+        pending.recv_wait_s = sum(a.elapsed_time(b) for a, b in pending.recv_waits) / 1e3
         if pending.status is not None and int(pending.status[0]) != 0:
             self._raise_on_device_failure()
         values = pending.host_f.tolist()
@@ -393,6 +420,8 @@ class PipelineParallel:
             "time/forward_time": ScalarMetric(clock.seconds("start", "forward_end"), reduce="max"),
             "time/backward_time": ScalarMetric(clock.seconds("forward_end", "backward_end"), reduce="max"),
             "time/host_step_time": ScalarMetric(time.perf_counter() - pending.host_start, reduce="max"),
+            # compute-stream idle time across the waits for stage-boundary tensors (0 without pipeline stages)
+            "time/pp_recv_wait": ScalarMetric(pending.recv_wait_s, reduce="max"),
         }
         counts = None
         if pending.n_local:
@@ -405,8 +434,7 @@ class PipelineParallel:
             torch.autograd.backward([ce_loss, moe_aux_loss])
         else:
             out = self.stage_outputs[microbatch_idx]
-            grad_buf, work = incoming
-            work.wait()
+            grad_buf = self._recv(incoming, self.dim.next_pp_rank)
             torch.autograd.backward([out, moe_aux_loss], [grad_buf, torch.ones_like(moe_aux_loss)])
         if not self.dim.is_pp_first_stage:
             self._send(self.stage_inputs[microbatch_idx].grad, self.dim.prev_pp_rank)

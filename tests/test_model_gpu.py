@@ -46,13 +46,13 @@ def test_forward_loss_and_gradients_match_fp32_oracle(experts, top_k, monkeypatc
     (want + oaux).backward()
     assert abs(loss.item() - want.item()) < 3e-2 * max(1.0, abs(want.item()))
     assert sum(s.tokens_per_expert.sum().item() for s in stats) == cfg.n_layers * x.numel() * top_k
+    # per tensor: ||g - g_oracle|| / ||g_oracle|| <= 3 % (bf16 activations and weights against fp32)
     errors = {}
     for (name, p), (_, q) in zip(model.named_parameters(), oracle.named_parameters()):
         assert p.grad is not None, name
-        denom = q.grad.abs().max().item() + 1e-6
-        errors[name] = (p.grad.float() - q.grad).abs().max().item() / denom
-    bad = {k: round(v, 3) for k, v in errors.items() if v >= 0.12}
-    assert not bad, f"relative gradient errors: {bad}"
+        errors[name] = ((p.grad.float() - q.grad).norm() / (q.grad.norm() + 1e-12)).item()
+    bad = {k: round(v, 4) for k, v in errors.items() if v > 0.03}
+    assert not bad, f"relative gradient errors above 3 %: {bad} (all: { {k: round(v, 4) for k, v in errors.items()} })"
 
 
 def test_training_reduces_loss_and_uses_native_kernels():
