@@ -71,7 +71,7 @@ struct Cfg {
   // operand stages of the streamed tiles; dK/dV at head dim 64 keeps two so that two CTAs still fit an SM's shared memory
   static constexpr int STAGES = (MODE == kDkv && DH == 64) ? 2 : 3;
   static constexpr int E_TILE = BR * BC * 2;
-  static constexpr int N_E = MODE == kDkv ? 2 : 1;
+  static constexpr int N_E = MODE == kDq ? 1 : 2;                // fwd: P of even / odd steps; dkv: P^T and dS^T
   static constexpr int OFF_R = 0;
   static constexpr int OFF_C = OFF_R + N_R * R_TILE;
   static constexpr int OFF_E = OFF_C + STAGES * 2 * C_TILE;
@@ -170,7 +170,9 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
   uint64_t* t_full_b = bars + 10;     // forward: score buffer 1
   uint64_t* e_full = bars + 11;       // 1 (one arrival per softmax warp)
   uint64_t* e_empty = bars + 12;      // 1
-  uint64_t* acc_full = bars + 13;     // 1
+  uint64_t* acc_full = bars + 13;     // 1 (forward: accumulator of even steps)
+  uint64_t* acc_full_b = bars + 14;   // forward: accumulator of odd steps
+  uint64_t* t_empty = bars + 15;      // backward: the softmax warps have read the scores into registers
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -201,6 +203,8 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
     mbar_init(e_full, SOFTMAX_THREADS / 32);  // one arrival per softmax warp
     mbar_init(e_empty, 1);
     mbar_init(acc_full, 1);
+    mbar_init(acc_full_b, 1);
+    mbar_init(t_empty, SOFTMAX_THREADS / 32);
     *abort_flag = 0u;
     fence_barrier_init();
     prefetch_tmap(&tm0);
@@ -267,64 +271,75 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
         if (lane == 0) {
           const int st = it % C::STAGES;
           const uint32_t cb = smem_u32(smem + C::OFF_C + st * 2 * C::C_TILE) + C::C_TILE;  // V
+          const uint32_t ep = (it & 1) ? e2 : e1;
 #pragma unroll
           for (int ks = 0; ks < BC / 16; ++ks)
-            umma_f16(tmem_base + C::COL_ACC1, make_desc(e1 + ks * 32, 16, 1024, 2u),
+            umma_f16(tmem_base + ((it & 1) ? C::COL_ACC2 : C::COL_ACC1), make_desc(ep + ks * 32, 16, 1024, 2u),
                      make_desc(cb + ks * 2 * C::SBO_RC, 16, C::SBO_RC, C::SWZ), idesc_acc, ks != 0 ? 1u : 0u);
           umma_commit(&c_empty[st]);
-          umma_commit(acc_full);
+          umma_commit((it & 1) ? acc_full_b : acc_full);
         }
         __syncwarp();
       }
     }
-    int stage = 0;
-    uint32_t phase = 0;
-    for (int it = 0; it < n_iter && ok && MODE != kFwd; ++it) {
-      if (!mbar_wait(&c_full[stage], phase, abort_flag, args.status, kKernelAttnFwd + MODE, 210 + stage)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t ca = smem_u32(smem + C::OFF_C + stage * 2 * C::C_TILE), cb = ca + C::C_TILE;
-      if (lane == 0) {
+    if (MODE != kFwd) {
+      // Backward.  T1 / T2 are single-buffered, but the softmax warps release them (t_empty) as soon as
+      // the scores sit in their registers, so the score products of step it+1 run under the softmax
+      // arithmetic of step it; only the accumulate products wait for the step's E tiles.
+      auto issue_t = [&](int it) -> bool {
+        const int st = it % C::STAGES;
+        if (!mbar_wait(&c_full[st], (it / C::STAGES) & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 210 + st)) return false;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t ca = smem_u32(smem + C::OFF_C + st * 2 * C::C_TILE), cb = ca + C::C_TILE;
 #pragma unroll
-        for (int ks = 0; ks < DH / 16; ++ks) {
-          umma_f16(tmem_base + C::COL_T1, make_desc(ra + ks * 32, 16, C::SBO_RC, C::SWZ), make_desc(ca + ks * 32, 16, C::SBO_RC, C::SWZ),
-                   idesc_t, ks != 0);
-        }
-        if (MODE != kFwd) {
+          for (int ks = 0; ks < DH / 16; ++ks)
+            umma_f16(tmem_base + C::COL_T1, make_desc(ra + ks * 32, 16, C::SBO_RC, C::SWZ), make_desc(ca + ks * 32, 16, C::SBO_RC, C::SWZ),
+                     idesc_t, ks != 0);
 #pragma unroll
-          for (int ks = 0; ks < DH / 16; ++ks) {
+          for (int ks = 0; ks < DH / 16; ++ks)
             umma_f16(tmem_base + C::COL_T2, make_desc(rb + ks * 32, 16, C::SBO_RC, C::SWZ), make_desc(cb + ks * 32, 16, C::SBO_RC, C::SWZ),
                      idesc_t, ks != 0);
-          }
+          umma_commit(t_full);
         }
-        umma_commit(t_full);
-      }
-      __syncwarp();
-      if (!mbar_wait(e_full, it & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 220)) { ok = false; break; }
-      tc_fence_after();
-      if (lane == 0) {
-        // Acc (+)= E . C_x with C_x read MN-major: 16 streamed rows per step = two 8-row groups
-        const uint32_t cx1 = (MODE == kDq) ? ca : cb;  // fwd: V, dq: K, dkv: dO
-        const uint32_t acc_on = (MODE == kFwd) ? 0u : (it != 0 ? 1u : 0u);
-#pragma unroll
-        for (int ks = 0; ks < BC / 16; ++ks) {
-          const uint32_t e_off = (ks >> 2) * (BR * 128) + (ks & 3) * 32;
-          umma_f16(tmem_base + C::COL_ACC1, make_desc(e1 + e_off, 16, 1024, 2u),
-                   make_desc(cx1 + ks * 2 * C::SBO_RC, 16, C::SBO_RC, C::SWZ), idesc_acc, (ks != 0) ? 1u : acc_on);
+        __syncwarp();
+        return true;
+      };
+      if (ok && n_iter > 0) ok = issue_t(0);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int st = it % C::STAGES;
+        if (it + 1 < n_iter) {
+          if (!mbar_wait(t_empty, it & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 215)) { ok = false; break; }
+          tc_fence_after();
+          if (!issue_t(it + 1)) { ok = false; break; }
         }
-        if (MODE == kDkv) {
+        if (!mbar_wait(e_full, it & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 220)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t ca = smem_u32(smem + C::OFF_C + st * 2 * C::C_TILE), cb = ca + C::C_TILE;
+          // Acc (+)= E . C_x with C_x read MN-major: 16 streamed rows per step = two 8-row groups
+          const uint32_t cx1 = (MODE == kDq) ? ca : cb;  // dq: K, dkv: dO
+          const uint32_t acc_on = it != 0 ? 1u : 0u;
 #pragma unroll
           for (int ks = 0; ks < BC / 16; ++ks) {
             const uint32_t e_off = (ks >> 2) * (BR * 128) + (ks & 3) * 32;
-            umma_f16(tmem_base + C::COL_ACC2, make_desc(e2 + e_off, 16, 1024, 2u),
-                     make_desc(ca + ks * 2 * C::SBO_RC, 16, C::SBO_RC, C::SWZ), idesc_acc, (ks != 0) ? 1u : acc_on);
+            umma_f16(tmem_base + C::COL_ACC1, make_desc(e1 + e_off, 16, 1024, 2u),
+                     make_desc(cx1 + ks * 2 * C::SBO_RC, 16, C::SBO_RC, C::SWZ), idesc_acc, (ks != 0) ? 1u : acc_on);
           }
+          if (MODE == kDkv) {
+#pragma unroll
+            for (int ks = 0; ks < BC / 16; ++ks) {
+              const uint32_t e_off = (ks >> 2) * (BR * 128) + (ks & 3) * 32;
+              umma_f16(tmem_base + C::COL_ACC2, make_desc(e2 + e_off, 16, 1024, 2u),
+                       make_desc(ca + ks * 2 * C::SBO_RC, 16, C::SBO_RC, C::SWZ), idesc_acc, (ks != 0) ? 1u : acc_on);
+            }
+          }
+          umma_commit(&c_empty[st]);
+          umma_commit(e_empty);
+          if (it == n_iter - 1) umma_commit(acc_full);
         }
-        umma_commit(&c_empty[stage]);
-        umma_commit(e_empty);
-        if (MODE == kFwd || it == n_iter - 1) umma_commit(acc_full);
+        __syncwarp();
       }
-      __syncwarp();
-      if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
     }
   } else {
     // ------------------------------------------------------------------ softmax / epilogue (2 x 128 threads)
@@ -352,19 +367,23 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
     }
     bool ok = true;
     if (MODE == kFwd) {
-      float alpha_prev = 0.f;
+      // The P.V product of step j lands in accumulator j & 1 and is folded into o_acc during step
+      // j + 2, so neither its latency nor the hand-offs around it sit on a step's critical path.
+      // alpha_j = exp(m_{j-1} - m_j) rescales what was folded before j; a1 / a2 hold it for the two
+      // steps whose products are still outstanding.
+      float a1 = 0.f, a2 = 0.f;
       float* mx = vec;  // [2 (step parity)][2 (warpgroup)][128]: the warpgroups' row maxima of a step
-      // fold this warpgroup's half of the P.V product of step `it` (already scaled to that step's row max)
-      auto fold_pv = [&](int it) -> bool {
-        if (!mbar_wait(acc_full, it & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 320)) return false;
+      // fold this warpgroup's half of the P.V product of step `j` (scaled to that step's row max)
+      auto fold_pv = [&](int j, float alpha_j) -> bool {
+        if (!mbar_wait((j & 1) ? acc_full_b : acc_full, (j >> 1) & 1, abort_flag, args.status, kKernelAttnFwd + MODE, 320)) return false;
         tc_fence_after();
 #pragma unroll
         for (int cc = 0; cc < HD; cc += 16) {
           uint32_t t[16];
-          tmem_ld_32x16(lane_addr + C::COL_ACC1 + col_half + cc, t);
+          tmem_ld_32x16(lane_addr + ((j & 1) ? C::COL_ACC2 : C::COL_ACC1) + col_half + cc, t);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) o_acc[cc + i] = o_acc[cc + i] * alpha_prev + __uint_as_float(t[i]);
+          for (int i = 0; i < 16; ++i) o_acc[cc + i] = o_acc[cc + i] * alpha_j + __uint_as_float(t[i]);
         }
         tc_fence_before();
         return true;
@@ -416,20 +435,22 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
           }
         }
         const float l_add = (l4[0] + l4[1]) + (l4[2] + l4[3]);
-        // the previous step's P.V finished long ago; folding it here keeps its latency off the loop
-        if (it > 0 && !fold_pv(it - 1)) { ok = false; continue; }
+        // the product of two steps ago finished long ago; its completion also frees this step's P tile
+        if (it > 1 && !fold_pv(it - 2, a2)) { ok = false; continue; }
         {
           float (&pr)[32] = *reinterpret_cast<float (*)[32]>(&t[0]);
-          write_e_chunk<32>(e1, r, wg * 32, pr, DT);
+          write_e_chunk<32>((it & 1) ? e2 : e1, r, wg * 32, pr, DT);
         }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(e_full);
         l_run = l_run * alpha + l_add;
         m_run = m_new;
-        alpha_prev = alpha;
+        a2 = a1;
+        a1 = alpha;
       }
-      if (ok && n_iter > 0) ok = fold_pv(n_iter - 1);
+      if (ok && n_iter > 1) ok = fold_pv(n_iter - 2, a2);
+      if (ok && n_iter > 0) ok = fold_pv(n_iter - 1, a1);
       // the two partial row sums meet (both were kept relative to the same running maximum)
       float* ls = vec + 4 * BR;
       ls[wg * BR + r] = l_run;
@@ -469,6 +490,11 @@ causal_attn_kernel(const __grid_constant__ CUtensorMap tm0, const __grid_constan
             tmem_ld_32x16(lane_addr + C::COL_T1 + cc, t1);
             tmem_ld_32x16(lane_addr + C::COL_T2 + cc, t2);
             tmem_ld_wait();
+            if (sub == 16) {  // this warp holds all its scores of the step: the next score products may overwrite T1 / T2
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(t_empty);
+            }
             float pv[16], ds[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
