@@ -9,8 +9,9 @@ launches after 3 warm-up launches, maximum over the ranks.  Inputs are larger th
 
 Rows:
   * `bucket_allreduce` (csrc/kernels/allreduce_adamw.cu) on 25 MiB and 256 MiB bf16 gradient
-    buckets, reduce-only and with the fused AdamW, on the multicast (`multimem`) path and on the
-    peer-load path, next to `dist.all_reduce` (NCCL) on the same buffer.  NVLink bytes per GPU per
+    buckets, reduce-only and with the fused AdamW, on the multicast (`multimem`) path (with the 64
+    CTAs training uses, and with 148) and on the peer-load path, next to `dist.all_reduce` (NCCL) on
+    the same buffer.  NVLink bytes per GPU per
     direction: one bucket (the slice exchange out, the reduced / updated values in).
   * `ep_dispatch` and `ep_push_rows` (csrc/kernels/ep_exchange.cu) on the expert-parallel model
     config (12288 tokens x top-2, 8 experts, d 512) and on the microbenchmark shapes (32768 tokens
@@ -71,8 +72,11 @@ def bench_allreduce(world, rank, dev, iters, flush, out):
 
     for mib in (25, 256):
         n = mib * (1 << 20) // 2
-        for multimem in (True, False):
+        for multimem, blocks in ((True, 64), (True, 148), (False, 64)):
+            # 64 CTAs is what training uses (the kernel shares the GPU with the backward pass); 148 shows the
+            # kernel alone on the machine
             os.environ["NT_MULTIMEM"] = "1" if multimem else "0"
+            os.environ["NT_ALLREDUCE_BLOCKS"] = str(blocks)
             engine = fused_allreduce.make_engine(dist.group.WORLD, world, dev)
             for adam in (False, True):
                 param = torch.nn.Parameter(torch.zeros(n, dtype=torch.bfloat16, device=dev))
@@ -88,7 +92,7 @@ def bench_allreduce(world, rank, dev, iters, flush, out):
                     engine.finish(red, bucket)
 
                 ms = timed(launch, iters, flush)
-                kind = ("multimem" if multimem and bucket._mc else "peer loads") + (" + AdamW" if adam else "")
+                kind = ("multimem" if multimem and bucket._mc else "peer loads") + f", {blocks} CTAs" + (" + AdamW" if adam else "")
                 out.append(row(f"bucket_allreduce ({kind})", f"{mib} MiB bf16, {world} ranks", ms, n * 2))
                 red.remove_hooks()
                 del red, param

@@ -34,6 +34,7 @@ namespace {
 
 constexpr int AR_THREADS = 512;
 constexpr int AR_MAX_RANKS = 16;
+constexpr int AR_UNROLL = 4;
 
 struct ArArgs {
   // gradients
@@ -167,45 +168,85 @@ bucket_allreduce_kernel(const ArArgs a) {
     const long long per = ((a.n / 8 + a.N - 1) / a.N) * 8;
     const long long lo = min(a.n, per * a.rank), hi = min(a.n, lo + per);
     const float inv_n = 1.f / static_cast<float>(a.N);
-    for (long long i = lo + (static_cast<long long>(blockIdx.x) * AR_THREADS + threadIdx.x) * 8; i < hi;
-         i += static_cast<long long>(gridDim.x) * AR_THREADS * 8) {
-      float g[8];
+    // Each thread keeps AR_UNROLL 16-byte reductions in flight: one `multimem.ld_reduce` (or one load per
+    // peer) has a round-trip latency of microseconds through the switch, and a single outstanding request
+    // per thread would cap the kernel far below the links.
+    const long long stride = static_cast<long long>(gridDim.x) * AR_THREADS * 8;
+    for (long long i0 = lo + (static_cast<long long>(blockIdx.x) * AR_THREADS + threadIdx.x) * 8; i0 < hi; i0 += stride * AR_UNROLL) {
+      uint4 q[AR_UNROLL];
+      float g[AR_UNROLL][8];
       if (a.grad_mc != nullptr) {
-        const uint4 q = a.dtype == 1 ? multimem_ld_reduce_bf16(a.grad_mc + i) : multimem_ld_reduce_f16(a.grad_mc + i);
-        unpack8(q, a.dtype, g);
+#pragma unroll
+        for (int u = 0; u < AR_UNROLL; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < hi) q[u] = a.dtype == 1 ? multimem_ld_reduce_bf16(a.grad_mc + i) : multimem_ld_reduce_f16(a.grad_mc + i);
+        }
+#pragma unroll
+        for (int u = 0; u < AR_UNROLL; ++u) unpack8(q[u], a.dtype, g[u]);
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) g[j] = 0.f;
-        for (int p = 0; p < a.N; ++p) {  // fixed order: identical sums whichever rank owns the slice
-          float f[8];
-          unpack8(*reinterpret_cast<const uint4*>(a.grad_peer[p] + i), a.dtype, f);
+        for (int u = 0; u < AR_UNROLL; ++u)
 #pragma unroll
-          for (int j = 0; j < 8; ++j) g[j] += f[j];
+          for (int j = 0; j < 8; ++j) g[u][j] = 0.f;
+        for (int p = 0; p < a.N; ++p) {  // fixed order: identical sums whichever rank owns the slice
+#pragma unroll
+          for (int u = 0; u < AR_UNROLL; ++u) {
+            const long long i = i0 + u * stride;
+            q[u] = i < hi ? *reinterpret_cast<const uint4*>(a.grad_peer[p] + i) : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int u = 0; u < AR_UNROLL; ++u) {
+            float f[8];
+            unpack8(q[u], a.dtype, f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) g[u][j] += f[j];
+          }
         }
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) g[j] *= inv_n;
-      uint4 out;
-      if (a.fuse_adam) {
-        float w[8];
+      for (int u = 0; u < AR_UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i >= hi) continue;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const long long s = i - a.state_lo + j;
-          float pw = a.master[s], mm = a.m[s], vv = a.v[s];
-          pw *= 1.f - a.lr * a.wd;
-          mm = a.beta1 * mm + (1.f - a.beta1) * g[j];
-          vv = a.beta2 * vv + (1.f - a.beta2) * g[j] * g[j];
-          pw -= (a.lr / bc1) * mm / (sqrtf(vv) * rsqrt_bc2 + a.eps);
-          a.master[s] = pw; a.m[s] = mm; a.v[s] = vv;
-          w[j] = pw;
+        for (int j = 0; j < 8; ++j) g[u][j] *= inv_n;
+        uint4 out;
+        if (a.fuse_adam) {
+          // the slice's fp32 state, 32 bytes at a time (slices start on multiples of 8 elements)
+          const long long s = i - a.state_lo;
+          float4 pw[2], mm[2], vv[2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            pw[h] = *reinterpret_cast<const float4*>(a.master + s + 4 * h);
+            mm[h] = *reinterpret_cast<const float4*>(a.m + s + 4 * h);
+            vv[h] = *reinterpret_cast<const float4*>(a.v + s + 4 * h);
+          }
+          float* pwf = reinterpret_cast<float*>(pw);
+          float* mmf = reinterpret_cast<float*>(mm);
+          float* vvf = reinterpret_cast<float*>(vv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            pwf[j] *= 1.f - a.lr * a.wd;
+            mmf[j] = a.beta1 * mmf[j] + (1.f - a.beta1) * g[u][j];
+            vvf[j] = a.beta2 * vvf[j] + (1.f - a.beta2) * g[u][j] * g[u][j];
+            pwf[j] -= (a.lr / bc1) * mmf[j] / (sqrtf(vvf[j]) * rsqrt_bc2 + a.eps);
+          }
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            *reinterpret_cast<float4*>(a.master + s + 4 * h) = pw[h];
+            *reinterpret_cast<float4*>(a.m + s + 4 * h) = mm[h];
+            *reinterpret_cast<float4*>(a.v + s + 4 * h) = vv[h];
+          }
+          float w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) w[j] = pwf[j];
+          out = pack8(w, a.dtype);
+          if (a.param_mc != nullptr) multimem_st(a.param_mc + i, out);
+          else for (int p = 0; p < a.N; ++p) *reinterpret_cast<uint4*>(a.param_peer[p] + i) = out;
+        } else {
+          out = pack8(g[u], a.dtype);
+          if (a.grad_mc != nullptr) multimem_st(a.grad_mc + i, out);
+          else for (int p = 0; p < a.N; ++p) *reinterpret_cast<uint4*>(a.grad_peer[p] + i) = out;
         }
-        out = pack8(w, a.dtype);
-        if (a.param_mc != nullptr) multimem_st(a.param_mc + i, out);
-        else for (int p = 0; p < a.N; ++p) *reinterpret_cast<uint4*>(a.param_peer[p] + i) = out;
-      } else {
-        out = pack8(g, a.dtype);
-        if (a.grad_mc != nullptr) multimem_st(a.grad_mc + i, out);
-        else for (int p = 0; p < a.N; ++p) *reinterpret_cast<uint4*>(a.grad_peer[p] + i) = out;
       }
     }
   }
@@ -261,6 +302,8 @@ void bucket_allreduce(at::Tensor grad_local, int64_t grad_mc, const at::Tensor& 
     TORCH_CHECK((whole || master->numel() == hi - lo) && m->numel() == master->numel() && v->numel() == master->numel(),
                 "bucket_allreduce: optimizer state must have the bucket's length or the owned slice's (", hi - lo, ")");
     a.state_lo = whole ? 0 : lo;
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(master->data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(m->data_ptr()) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(v->data_ptr()) % 16 == 0, "bucket_allreduce: optimizer state must be 16-byte aligned");
     const auto* pp = param_peers.data_ptr<int64_t>();
     for (int i = 0; i < world; ++i) a.param_peer[i] = reinterpret_cast<uint16_t*>(pp[i]);
     a.master = master->data_ptr<float>();

@@ -249,7 +249,19 @@ ep_push_rows_kernel(const PushArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int warps = EP_THREADS / 32;
     const long long rows = min(static_cast<long long>(seg_start[a.E]), a.src_rows);
-    for (long long r = static_cast<long long>(blockIdx.x) * warps + warp; r < rows; r += static_cast<long long>(gridDim.x) * warps) {
+    // Rows are sorted by destination, and every rank would walk the destinations in the same order: all
+    // ranks storing into rank 0 first, then into rank 1, ... - one receiver's links busy at a time.  Each
+    // rank therefore starts its walk at the first row bound for rank (me + 1) and wraps around, so at any
+    // moment the ranks address different receivers.
+    long long rot = 0;
+    {
+      const int first = (me + 1) % a.ep;
+      const int g0 = a.direction == 0 ? first * a.E_loc : first;  // first segment whose destination is `first`
+      rot = min(static_cast<long long>(seg_start[g0]), rows);
+    }
+    for (long long r0 = static_cast<long long>(blockIdx.x) * warps + warp; r0 < rows; r0 += static_cast<long long>(gridDim.x) * warps) {
+      long long r = r0 + rot;
+      if (r >= rows) r -= rows;
       int lo = 0, hi = a.E;  // last segment with seg_start <= r
       while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
