@@ -312,6 +312,9 @@ def run_ours(args, config: str) -> dict:
 
     for i in range(max(args.warmup, 3)):  # two ordinary steps, then the step that captures the CUDA graph
         device_step(i)
+        if os.environ.get("NT_BENCH_SYNC_WARMUP") == "1":  # debugging aid: name the warm-up step a fault belongs to
+            torch.cuda.synchronize()
+            print(f"[rank {dims.global_rank}] warm-up step {i} done, status {native.read_status(False)}", flush=True)
     torch.cuda.synchronize()
     if ep > 1 and os.environ.get("NT_FUSED_EP", "1") != "0" and _paths(model, reducers, dims)["ep"] != "fused_p2p":
         raise RuntimeError("the fused expert-parallel exchange could not be set up on this multi-GPU run; "

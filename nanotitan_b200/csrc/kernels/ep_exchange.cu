@@ -145,12 +145,17 @@ ep_dispatch_kernel(const DispatchArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int warps = EP_THREADS / 32;
     for (long long t = static_cast<long long>(blockIdx.x) * warps + warp; t < a.tokens; t += static_cast<long long>(gridDim.x) * warps) {
-      int my_slot = 0, my_e = 0;
+      int my_slot = 0, my_e = -1;
       if (lane < a.k) {
         my_slot = a.slot_of[t * a.k + lane];
         my_e = a.idx[t * a.k + lane];
-        a.packed_token[my_slot] = static_cast<int>(t);
-        a.packed_gate[my_slot] = a.gates[t * a.k + lane];
+        if (my_slot < 0 || my_slot >= a.tokens * a.k) {  // a slot outside the packed range: skip the choice and report
+          report_status(xr.status, kStatusBounds, kKernelEpDispatch, 200000u + static_cast<uint32_t>(lane));
+          my_e = -1;
+        } else {
+          a.packed_token[my_slot] = static_cast<int>(t);
+          a.packed_gate[my_slot] = a.gates[t * a.k + lane];
+        }
       }
       const uint4* src = a.x + t * a.vec_per_row;
       for (int j = 0; j < a.k; ++j) {

@@ -29,7 +29,7 @@ template <typename T, typename WT>
 __global__ void __launch_bounds__(RT_WARPS * 32)
 router_topk_kernel(const T* __restrict__ x, const WT* __restrict__ w, float* __restrict__ gates, int* __restrict__ idx,
                    float* __restrict__ probs, int* __restrict__ counts, float* __restrict__ prob_parts,
-                   long long tokens, int d, int E, int k) {
+                   long long tokens, int d, int E, int k, StatusWord* __restrict__ status) {
   extern __shared__ float sx[];  // [RT_WARPS][RT_TOK][d] token rows as fp32
   __shared__ int s_counts[RT_MAX_E];
   __shared__ float s_psum[RT_WARPS][RT_MAX_E];
@@ -115,11 +115,23 @@ router_topk_kernel(const T* __restrict__ x, const WT* __restrict__ w, float* __r
           const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
           if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
         }
+        if (best_e >= E) {
+          // No expert has a comparable probability: the token row holds NaN (an earlier kernel of the
+          // step failed).  Route it to expert j with a neutral weight and say so, instead of using
+          // the sentinel as an index.
+          best_e = j;
+          best = 0.f;
+          if (lane == 0) report_status(status, kStatusBadArgument, kKernelPack, static_cast<uint32_t>(tok));
+        }
 #pragma unroll
         for (int s = 0; s < RT_SLOTS; ++s)
           if (s * 32 + lane == best_e) p[s] = -2.f;  // remove from later rounds
         taken_sum += best;
         if (lane == j) { my_gate = best; my_e = best_e; }
+      }
+      if (!(taken_sum > 0.f)) {  // all-NaN row: equal weights
+        my_gate = 1.f;
+        taken_sum = static_cast<float>(k);
       }
       if (lane < k) {
         gates[tok * k + lane] = my_gate / taken_sum;
@@ -315,7 +327,7 @@ std::vector<at::Tensor> router_topk(const at::Tensor& x, const at::Tensor& w, in
         auto kernel = router_topk_kernel<x_t, scalar_t>;
         if (smem > 48 * 1024) NT_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         kernel<<<grid, RT_WARPS * 32, smem, stream>>>(x.data_ptr<x_t>(), w.data_ptr<scalar_t>(), gates.data_ptr<float>(), idx.data_ptr<int>(),
-            probs.data_ptr<float>(), counts.data_ptr<int>(), parts.data_ptr<float>(), tokens, d, E, static_cast<int>(k));
+            probs.data_ptr<float>(), counts.data_ptr<int>(), parts.data_ptr<float>(), tokens, d, E, static_cast<int>(k), device_status_word());
       });
     });
     NT_KERNEL_CHECK();

@@ -261,25 +261,54 @@ def cross_entropy(logits, targets):
     return _CrossEntropy.apply(logits, targets)
 
 
+def _ce_chunk_rows() -> int:
+    """Rows per panel of the unembed + loss op (`NT_CE_CHUNK_ROWS`, 0 = one panel).  One panel is the
+    fastest form and keeps a [rows, vocab] bf16 buffer alive for the duration of the op (3.1 GB at
+    30720 x 50304); panels of e.g. 4096 rows bound that buffer (0.41 GB) at the price of accumulating
+    the weight gradient in fp32 across panels."""
+    try:
+        return max(0, int(os.environ.get("NT_CE_CHUNK_ROWS", "0")))
+    except ValueError:
+        return 0
+
+
 class _LinearCrossEntropy(torch.autograd.Function):
-    """mean CE(x @ w^T, targets) with w [V, d].  The bf16 logits live in one padded buffer that
-    the loss kernel overwrites with their gradient; dx and dw are formed at once, so backward
-    only scales them."""
+    """mean CE(x @ w^T, targets) with w [V, d].  The bf16 logits of a panel of rows live in one padded
+    buffer that the loss kernel overwrites with their gradient; dx and dw are formed at once, so
+    backward only scales them.  With several panels the buffer is reused and dw accumulates in fp32."""
 
     @staticmethod
     def forward(ctx, x, w, targets):
         ext = get_ext()
         rows, vocab = x.shape[0], w.shape[0]
         ld = (vocab + 63) // 64 * 64
-        logits = torch.empty(rows, ld, dtype=x.dtype, device=x.device)
-        view = logits[:, :vocab]
-        gemm_tc(x, False, [w], False, [view])  # w [V, d]: K-major B
-        row_loss = ext.cross_entropy_fwd_bwd(logits, targets.contiguous(), vocab, 1.0 / max(rows, 1), True)
-        loss = row_loss.sum() / max(rows, 1)
+        panel = _ce_chunk_rows()
+        panel = rows if panel <= 0 or panel >= rows else (panel + 127) // 128 * 128
+        targets = targets.contiguous()
+        logits = torch.empty(min(panel, rows), ld, dtype=x.dtype, device=x.device)
         dx = torch.empty_like(x)
-        gemm_tc(view, False, [w], True, [dx])  # reduction over V: w [V, d] is MN-major here
-        dw = torch.empty_like(w)
-        gemm_tc(view, True, [x], True, [dw])  # dlogits^T x
+        inv_rows = 1.0 / max(rows, 1)
+        if panel >= rows:
+            view = logits[:, :vocab]
+            gemm_tc(x, False, [w], False, [view])  # w [V, d]: K-major B
+            row_loss = ext.cross_entropy_fwd_bwd(logits, targets, vocab, inv_rows, True)
+            loss = row_loss.sum() * inv_rows
+            gemm_tc(view, False, [w], True, [dx])  # reduction over V: w [V, d] is MN-major here
+            dw = torch.empty_like(w)
+            gemm_tc(view, True, [x], True, [dw])  # dlogits^T x
+        else:
+            dw32 = torch.empty(w.shape, dtype=torch.float32, device=x.device)
+            loss_sum = torch.zeros((), dtype=torch.float32, device=x.device)
+            for lo in range(0, rows, panel):
+                hi = min(rows, lo + panel)
+                view = logits[: hi - lo, :vocab]
+                xs = x[lo:hi]
+                gemm_tc(xs, False, [w], False, [view])
+                loss_sum += ext.cross_entropy_fwd_bwd(logits[: hi - lo], targets[lo:hi], vocab, inv_rows, True).sum()
+                gemm_tc(view, False, [w], True, [dx[lo:hi]])
+                gemm_tc(view, True, [xs], True, [dw32], accumulate=lo > 0)
+            loss = loss_sum * inv_rows
+            dw = dw32.to(w.dtype)
         ctx.save_for_backward(dx, dw, w)
         return loss
 

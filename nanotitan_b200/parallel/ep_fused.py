@@ -18,10 +18,17 @@ gradient and the combine backward read), so they come from a pool of symmetric b
 hands out a free buffer (allocating - a collective over the group - when none fits), `release`
 returns it when the layer's backward has used it, `reset` returns everything at the start of a
 step.  Every rank runs the same layers in the same order, so the pools evolve identically and a
-buffer is the same symmetric allocation on every rank.  Expert-side buffers hold
-`capacity_factor x` this rank's own assignment count (at most ep x, the true worst case); rows
-beyond that are dropped by the kernel, which records it in the device status word, and the step
-then fails with a message naming `NT_EP_CAPACITY_FACTOR`.
+buffer is the same symmetric allocation on every rank.
+
+Capacity.  Nothing on the host knows how many rows a rank will receive (the counts stay on the
+device), so expert-side buffers are sized for the worst case, ep x this rank's own assignment
+count, and no row is ever dropped - the reference's semantics.  That is not a formality: with
+random-initialised weights the deeper layers of the 16-layer benchmark model route 60-70 % of all
+tokens to two experts, so one rank of an ep = 4 group receives 2.7 x its fair share.
+`NT_EP_CAPACITY_FACTOR=f` bounds the buffers at f x the fair share for runs whose routing is
+known to be balanced (a trained router with the load-balancing loss); rows beyond the bound are
+then dropped by the kernel, which records it in the device status word, and the step fails with
+a message naming the variable.
 
 Ordering.  Only the dispatch kernel opens with a cross-rank barrier (it carries the counts).  The
 other three transfers start without one: each writes a buffer whose last readers on the peers were
@@ -67,7 +74,7 @@ class FusedExchange:
         self.E_loc = num_experts // self.ep
         self.wait_ms = float(os.environ.get("NT_COMM_WAIT_MS", "60000"))
         self.blocks = int(os.environ.get("NT_EP_BLOCKS", "128"))
-        self.capacity_factor = float(os.environ.get("NT_EP_CAPACITY_FACTOR", "2.0"))
+        self.capacity_factor = float(os.environ.get("NT_EP_CAPACITY_FACTOR", "0"))  # 0 = worst case (ep x)
         self._handles = {}
         self.flags = self._alloc(FLAG_WORDS, torch.int32)
         self.flags.zero_()
@@ -131,8 +138,11 @@ class FusedExchange:
 
     def capacity_rows(self, assignments: int) -> int:
         """Rows an expert rank's buffers hold for a layer in which every rank routes `assignments` rows."""
+        worst = max(128, self.ep * assignments)
+        if self.capacity_factor <= 0:
+            return worst
         bounded = int(math.ceil(self.capacity_factor * assignments / 128.0)) * 128
-        return max(128, min(self.ep * assignments, bounded))
+        return max(128, min(worst, bounded))
 
     # ------------------------------------------------------------------ primitives
     def allgather_counts(self, counts: torch.Tensor) -> torch.Tensor:

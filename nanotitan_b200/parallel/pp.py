@@ -130,6 +130,11 @@ class PipelineParallel:
         if not ext.have_ext():
             return
         code, kernel, detail, count = ext.get_ext().read_status(True)
+        if code == 2 and kernel == 5 and detail >= 100000:
+            raise RuntimeError(
+                f"expert-parallel dispatch: expert {detail % 100000} received more rows than the staging buffers hold "
+                f"({count} rows dropped on this rank); NT_EP_CAPACITY_FACTOR bounds those buffers - unset it (worst-case "
+                "buffers, no drops) or raise it")
         if code != 0:
             raise RuntimeError(
                 f"a device-side wait or check failed during this step (code={code}, kernel={kernel}, "
