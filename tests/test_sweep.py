@@ -1,32 +1,77 @@
+"""The sweep runner: grid expansion over flat config maps, run names, TOML emission, launch sizing."""
+import tomllib
 from pathlib import Path
 
+import pytest
+
+from nanotitan_b200 import sweep
 from nanotitan_b200.config import AppConfig, load_config
-from nanotitan_b200.sweep import build_runs, dump_toml, launch_command, main
+
+SWEEP = Path("configs/sweep_hparams.toml")
 
 
-def test_checked_in_sweep_builds_valid_named_runs():
-    _, runs = build_runs(Path("configs/sweep_hparams.toml"))
+@pytest.fixture(scope="module")
+def runs():
+    return sweep.build_runs(SWEEP)[1]
+
+
+def test_flat_form_round_trips():
+    nested = {"a": 1, "t": {"x": "s", "u": {"deep": [1, 2]}}, "b": False}
+    flat = sweep.flatten(nested)
+    assert flat == {"a": 1, "t.x": "s", "t.u.deep": [1, 2], "b": False}
+    assert sweep.unflatten(flat) == nested
+
+
+def test_grid_is_the_cartesian_product_in_file_order():
+    points = list(sweep.grid_points({"optim.lr": [1, 2, 3], "model.dtype": ["a", "b"]}))
+    assert len(points) == 6
+    assert points[0] == {"optim.lr": 1, "model.dtype": "a"} and points[1] == {"optim.lr": 1, "model.dtype": "b"}
+
+
+def test_checked_in_sweep_expands_to_valid_uniquely_named_configs(runs):
+    # 6 learning rates x 3 dtypes
     assert len(runs) == 18
-    assert runs[0][0].endswith("optim-lr-0.01__model-dtype-bfloat16")
-    assert len({name for name, _ in runs}) == len(runs)
-    for name, config in runs:
-        assert AppConfig.model_validate(config).run_name == name
+    names = [name for name, _ in runs]
+    assert len(set(names)) == 18
+    assert names[0].endswith("__optim-lr-0.01__model-dtype-bfloat16")
+    for name, cfg in runs:
+        validated = AppConfig.model_validate(cfg)
+        assert validated.run_name == name
+        assert validated.runtime.num_expert == validated.model.num_experts
 
 
-def test_generated_toml_round_trips(tmp_path):
-    _, runs = build_runs(Path("configs/sweep_hparams.toml"))
-    out = tmp_path / "generated.toml"
-    out.write_text(dump_toml(runs[0][1]), encoding="utf-8")
-    assert load_config(out).run_name == runs[0][0]
+def test_emitted_toml_loads_back_as_the_same_config(tmp_path, runs):
+    name, cfg = runs[7]
+    text = sweep.dump_toml(cfg)
+    assert tomllib.loads(text)["model"]["dtype"] == cfg["model"]["dtype"]
+    path = tmp_path / "run.toml"
+    path.write_text(text, encoding="utf-8")
+    loaded = load_config(path)
+    assert loaded.run_name == name
+    assert loaded.model_dump(mode="json") == AppConfig.model_validate(cfg).model_dump(mode="json")
 
 
-def test_launch_world_size_counts_ep():
-    _, runs = build_runs(Path("configs/sweep_hparams.toml"))
+def test_unknown_sweep_key_is_rejected(tmp_path):
+    bad = tmp_path / "bad.toml"
+    bad.write_text(f'base_config = "{Path("configs/dist.toml").resolve()}"\n[parameters]\n"optim.momentum" = [0.9]\n')
+    with pytest.raises(KeyError, match="optim.momentum"):
+        sweep.build_runs(bad)
+
+
+def test_launch_uses_one_process_per_rank_of_all_three_dimensions(runs):
     cfg = runs[0][1]
     cfg["runtime"].update(dp_size=2, pp_size=2, ep_size=2)
-    assert "--nproc-per-node=8" in launch_command(cfg, Path("x.toml"), "INFO")
+    cmd = sweep.launch_command(cfg, Path("x.toml"), "INFO")
+    assert "--nproc-per-node=8" in cmd and "@x.toml" in cmd and "--log.level=INFO" in cmd
 
 
-def test_dry_run_launches_nothing(capsys):
-    assert main(["configs/sweep_hparams.toml", "--dry-run"]) == 0
-    assert "[18/18]" in capsys.readouterr().out
+def test_dry_run_prints_every_run_and_starts_none(capsys):
+    assert sweep.main([str(SWEEP), "--dry-run"]) == 0
+    out = capsys.readouterr().out
+    assert "[18/18]" in out and out.count("torch.distributed.run") == 18
+
+
+def test_reference_entry_path_is_importable():
+    import scripts.sweep as entry
+
+    assert entry.build_runs is sweep.build_runs and entry.main is sweep.main
