@@ -131,9 +131,43 @@ def main(argv=None) -> None:
     peak = cfg.hardware.peak_flops_tflops_per_gpu * 1e12
     # data is sharded over dp*ep ranks (the reference counts dp only, src/train.py:157)
     tokens_per_step = cfg.trainer.per_device_batch_size * dims.data_world_size * cfg.model.max_seq_len
+    # Step metrics are reduced over a host-side (gloo) group: the values are already on the host when
+    # they are reduced, and a collective on the compute stream would have to wait for the step that
+    # was launched in the meantime.
+    metrics_group = None
+    if world_size > 1 and device.type == "cuda":
+        import torch.distributed as dist
+
+        metrics_group = dist.new_group(backend="gloo")
+
+    def report(entry) -> None:
+        """Collect, reduce and log the metrics of a step that was launched earlier."""
+        index, seen, pending = entry
+        metrics = pending.result()
+        metrics["train/tokens_per_step"] = ScalarMetric(tokens_per_step, reduce="none")
+        metrics["train/total_tokens_seen"] = ScalarMetric(seen, reduce="none")
+        if hasattr(optimizer, "last_grad_norm"):
+            metrics["train/grad_norm"] = ScalarMetric(optimizer.last_grad_norm(), reduce="max")
+        metrics = reduce_metrics(metrics, torch.device("cpu") if metrics_group is not None else device, group=metrics_group)
+        metrics["train/tokens_per_second"] = metrics["train/tokens_per_step"] / metrics["time/step_time"]
+        metrics["train/ce_loss"] = metrics["train/ce_loss"] / dims.data_world_size
+        metrics["train/lb_loss"] = metrics["train/lb_loss"] / dims.data_world_size
+        if peak > 0:
+            metrics["perf/mfu"] = metrics["train/tokens_per_second"] * flops_per_token / (peak * world_size)
+        if dims.local_rank == 0:
+            logger.info("step %d | ce %.4f | lb %.4f | %.0f tok/s | %.1f ms",
+                        index, metrics["train/ce_loss"], metrics["train/lb_loss"],
+                        metrics["train/tokens_per_second"], 1e3 * metrics["time/step_time"])
+            metrics_logger.log(step=index, metrics=metrics)
+
     logger.info("Attempting to begin training")
     try:
         epoch = 0
+        # On GPUs the loop runs one step ahead of its own reporting: step i+1 is launched before the metrics
+        # of step i are collected, so reading the losses never leaves the device idle.  On CPU a step's
+        # collectives block the host, there is nothing to overlap, and every step is reported at once.
+        run_ahead = device.type == "cuda"
+        in_flight = None
         with profiler as prof:
             while step < cfg.max_steps:
                 if hasattr(train_loader.sampler, "set_epoch"):
@@ -142,27 +176,14 @@ def main(argv=None) -> None:
                 for batch in train_loader:
                     progressed = True
                     check_peers()
-                    metrics = pp.train_step(model, batch, optimizer)
+                    pending = pp.train_step(model, batch, optimizer, collect_metrics="deferred")
                     tokens_seen += tokens_per_step
-                    metrics["train/tokens_per_step"] = ScalarMetric(tokens_per_step, reduce="none")
-                    metrics["train/total_tokens_seen"] = ScalarMetric(tokens_seen, reduce="none")
-                    if hasattr(optimizer, "last_grad_norm"):
-                        metrics["train/grad_norm"] = ScalarMetric(optimizer.last_grad_norm(), reduce="max")
-                    metrics = reduce_metrics(metrics, device)
-                    metrics["train/tokens_per_second"] = (
-                        metrics["train/tokens_per_step"] / metrics["time/step_time"]
-                    )
-                    metrics["train/ce_loss"] = metrics["train/ce_loss"] / dims.data_world_size
-                    metrics["train/lb_loss"] = metrics["train/lb_loss"] / dims.data_world_size
-                    if peak > 0:
-                        metrics["perf/mfu"] = (
-                            metrics["train/tokens_per_second"] * flops_per_token / (peak * world_size)
-                        )
-                    if dims.local_rank == 0:
-                        logger.info("step %d | ce %.4f | lb %.4f | %.0f tok/s | %.1f ms",
-                                    step, metrics["train/ce_loss"], metrics["train/lb_loss"],
-                                    metrics["train/tokens_per_second"], 1e3 * metrics["time/step_time"])
-                        metrics_logger.log(step=step, metrics=metrics)
+                    if in_flight is not None:
+                        report(in_flight)
+                    in_flight = (step, tokens_seen, pending)
+                    if not run_ahead:
+                        report(in_flight)
+                        in_flight = None
                     step += 1
                     prof.step()
                     if heartbeat is not None:
@@ -176,6 +197,9 @@ def main(argv=None) -> None:
                 epoch += 1
                 if not progressed:
                     raise RuntimeError("the training loader produced no batch (dataset too small)")
+            if in_flight is not None:
+                report(in_flight)
+                in_flight = None
         if cfg.checkpoint.dir:
             check_peers()
             save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg)

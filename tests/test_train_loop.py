@@ -1,0 +1,82 @@
+"""The training entrypoint end to end on CPU: every step is reported once, in order, under the
+reference's metric names; a run resumes from its own checkpoint; two gloo ranks agree on the metrics."""
+from pathlib import Path
+
+import pytest
+
+from tests.conftest import run_distributed
+from tests.helpers import tiny_app_cfg
+
+
+def _write_cfg(tmp, name, **over):
+    from nanotitan_b200.sweep import dump_toml
+
+    cfg = tiny_app_cfg(**over.pop("layout", {})).model_dump(mode="json")
+    cfg.update(over)
+    path = Path(tmp) / name
+    path.write_text(dump_toml(cfg), encoding="utf-8")
+    return path
+
+
+def _run_main(path, logged, extra=()):
+    from nanotitan_b200 import metrics, train
+
+    plain = metrics.MetricsLogger.log
+
+    def spy(self, step, metrics):
+        logged.append((step, dict(metrics)))
+        return plain(self, step, metrics)
+
+    metrics.MetricsLogger.log = spy
+    try:
+        train.main([str(path), "--synthetic-data", "--log.level", "WARNING", *extra])
+    finally:
+        metrics.MetricsLogger.log = plain
+
+
+def test_every_step_is_reported_once_in_order_with_the_reference_metric_names(tmp_path, monkeypatch):
+    monkeypatch.chdir(tmp_path)
+    path = _write_cfg(tmp_path, "run.toml", max_steps=4)
+    logged = []
+    _run_main(path, logged)
+    assert [s for s, _ in logged] == [0, 1, 2, 3]
+    names = set(logged[0][1])
+    for want in ("train/ce_loss", "train/lb_loss", "train/total_loss", "time/step_time", "time/forward_time",
+                 "train/tokens_per_step", "train/total_tokens_seen", "train/tokens_per_second", "moe/layer_00/route_frac_dist"):
+        assert want in names, want
+    seen = [m["train/total_tokens_seen"] for _, m in logged]
+    per_step = logged[0][1]["train/tokens_per_step"]
+    assert seen == [per_step * (i + 1) for i in range(4)]
+    assert all(m["train/ce_loss"] == m["train/ce_loss"] for _, m in logged)  # no NaN
+
+
+def test_a_run_resumes_from_its_own_checkpoint(tmp_path, monkeypatch):
+    monkeypatch.chdir(tmp_path)
+    ckpt = {"dir": str(tmp_path / "ckpt"), "every_steps": 2, "resume": False}
+    first = _write_cfg(tmp_path, "a.toml", max_steps=2, checkpoint=ckpt)
+    logged = []
+    _run_main(first, logged)
+    assert [s for s, _ in logged] == [0, 1]
+    second = _write_cfg(tmp_path, "b.toml", max_steps=4, checkpoint=dict(ckpt, resume=True))
+    more = []
+    _run_main(second, more)
+    assert [s for s, _ in more] == [2, 3]
+    assert more[0][1]["train/total_tokens_seen"] == 3 * logged[0][1]["train/tokens_per_step"]
+
+
+def _two_rank_worker(rank, world, tmp):
+    import os
+
+    os.chdir(tmp)
+    path = _write_cfg(tmp, f"r{rank}.toml", max_steps=3, layout=dict(dp=2, batch=2))
+    logged = []
+    _run_main(path, logged)
+    if rank == 0:
+        assert [s for s, _ in logged] == [0, 1, 2]
+        # tokens per step count both data-parallel ranks
+        assert logged[0][1]["train/tokens_per_step"] % 2 == 0 and logged[0][1]["train/tokens_per_step"] > 0
+
+
+@pytest.mark.distributed
+def test_two_data_parallel_ranks_train_through_the_entrypoint(tmp_path):
+    run_distributed(_two_rank_worker, 2, str(tmp_path))
