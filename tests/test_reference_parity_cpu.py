@@ -73,3 +73,35 @@ def test_same_weights_give_the_same_logits_statistics_and_gradients(experts, top
     for name, p in ref.named_parameters():
         assert mine[name].grad is not None, name
         torch.testing.assert_close(mine[name].grad, p.grad, rtol=2e-4, atol=2e-5, msg=lambda m, n=name: f"{n}: {m}")
+
+
+def test_training_trajectories_agree_over_twenty_steps():
+    """Reference model + its optimizer (torch AdamW, weight decay 0.1) against this model + FusedAdamW
+    (flat buckets, fp32 master weights), same weights and batches: the loss curves coincide."""
+    from nanotitan_b200.ops.adamw import FusedAdamW
+
+    ref = _reference_model(4, 2)
+    ours = _our_model(4, 2)
+    ours.load_state_dict(ref.state_dict())
+    ref_opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, weight_decay=0.1)
+    our_opt = FusedAdamW(ours.parameters(), lr=1e-3, weight_decay=0.1)
+
+    def loss_of(model, ids, targets):
+        logits, stats = model(ids)
+        ce = torch.nn.functional.cross_entropy(logits.reshape(-1, logits.size(-1)), targets.reshape(-1))
+        return ce + torch.stack([s.aux_loss for s in stats]).mean(), ce
+
+    gen = torch.Generator().manual_seed(21)
+    curve_ref, curve_ours = [], []
+    for _ in range(20):
+        ids = torch.randint(0, MODEL["vocab_size"], (4, MODEL["max_seq_len"]), generator=gen)
+        targets = torch.roll(ids, -1, dims=1)
+        for model, opt, curve in ((ref, ref_opt, curve_ref), (ours, our_opt, curve_ours)):
+            opt.zero_grad()
+            total, ce = loss_of(model, ids, targets)
+            total.backward()
+            opt.step()
+            curve.append(ce.item())
+    assert curve_ref[-1] < curve_ref[0], "the reference did not learn; the comparison would be empty"
+    for step, (a, b) in enumerate(zip(curve_ours, curve_ref)):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(b)), f"step {step}: ours {a} reference {b}"
