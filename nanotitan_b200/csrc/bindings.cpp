@@ -53,6 +53,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("combine_fwd", &nt::combine_fwd);
   m.def("combine_bwd", &nt::combine_bwd);
   m.def("pack_bwd", &nt::pack_bwd);
+  m.def("symm_heap_open", &nt::symm_heap_open, py::arg("job"), py::arg("rank"), py::arg("world"), py::arg("device"),
+        py::arg("timeout_ms"), "Open this rank's end of a symmetric heap (collective over the ranks of one machine)");
+  m.def("symm_heap_alloc", &nt::symm_heap_alloc, py::arg("heap"), py::arg("bytes"), py::arg("multicast"),
+        "Collective allocation -> (byte tensor over this rank's piece, every rank's address, multicast address, id)");
+  m.def("symm_heap_free", &nt::symm_heap_free);
+  m.def("symm_heap_close", &nt::symm_heap_close);
   m.def("bounded_wait_probe", &nt::bounded_wait_probe, "Let a bounded device wait run out; returns the number of threads that gave up");
   m.def("read_status", &nt::read_status, py::arg("clear") = true, "[code, kernel, detail, count] of the device status word");
   m.def("status_word_tensor", &nt::status_word_tensor);

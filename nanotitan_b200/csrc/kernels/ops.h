@@ -3,6 +3,7 @@
 #include <ATen/ATen.h>
 
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "status.h"
@@ -15,6 +16,15 @@ std::vector<int64_t> read_status(bool clear);
 at::Tensor status_word_tensor();  // [code, kernel, detail, count]
 
 int64_t bounded_wait_probe(double limit_ms);  // probe.cu: makes a bounded device wait run out, on purpose
+
+// ---- symmetric heap (runtime/symmetric_heap.h behind integer handles; runtime/symmetric_heap_torch.cpp).
+//   open: collective over the ranks of one machine that share `job`; alloc (collective) returns this rank's
+//   piece as a byte tensor, every rank's address of the allocation, the multicast address (0: none) and the
+//   allocation's id; free and close are collective too.
+int64_t symm_heap_open(const std::string& job, int64_t rank, int64_t world, int64_t device, int64_t timeout_ms);
+std::tuple<at::Tensor, std::vector<int64_t>, int64_t, int64_t> symm_heap_alloc(int64_t heap, int64_t bytes, bool multicast);
+void symm_heap_free(int64_t heap, int64_t allocation);
+void symm_heap_close(int64_t heap);
 
 // ---- tcgen05 GEMM (gemm_tc.cu).
 //   A: 2-D; a_mn=false -> [M, K] rows contiguous in K, a_mn=true -> [K, M] rows contiguous in M.

@@ -36,7 +36,7 @@ enqueued before a kernel that ended with a cross-rank barrier this rank has alre
 dispatch of the same layer, or the previous transfer of the same backward), so those reads are over.
 All transfers end with a barrier: every rank's rows have landed when the kernel completes.
 
-Symmetric memory and its rendezvous come from `torch.distributed._symmetric_memory`.
+Symmetric memory comes from a provider in `parallel/symm_memory.py` (torch's, or this library's own heap).
 """
 from __future__ import annotations
 
@@ -65,9 +65,9 @@ class _SymmBuffer:
 
 class FusedExchange:
     def __init__(self, group, num_experts: int, device: torch.device):
-        import torch.distributed._symmetric_memory as symm_mem
+        from nanotitan_b200.parallel.symm_memory import make_provider
 
-        self.symm_mem, self.group, self.device = symm_mem, group, device
+        self.symm, self.group, self.device = make_provider(group, device), group, device
         self.ep = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.E = num_experts
@@ -75,7 +75,6 @@ class FusedExchange:
         self.wait_ms = float(os.environ.get("NT_COMM_WAIT_MS", "60000"))
         self.blocks = int(os.environ.get("NT_EP_BLOCKS", "128"))
         self.capacity_factor = float(os.environ.get("NT_EP_CAPACITY_FACTOR", "0"))  # 0 = worst case (ep x)
-        self._handles = {}
         self.flags = self._alloc(FLAG_WORDS, torch.int32)
         self.flags.zero_()
         self.flag_peers = self._peers(self.flags)
@@ -93,12 +92,10 @@ class FusedExchange:
 
     # ------------------------------------------------------------------ symmetric memory
     def _alloc(self, numel, dtype):
-        t = self.symm_mem.empty(numel, dtype=dtype, device=self.device)
-        self._handles[t.data_ptr()] = self.symm_mem.rendezvous(t, self.group)
-        return t
+        return self.symm.empty(numel, dtype)
 
     def _peers(self, t):
-        return torch.tensor(list(self._handles[t.data_ptr()].buffer_ptrs), dtype=torch.int64)
+        return torch.tensor(self.symm.peer_ptrs(t), dtype=torch.int64)
 
     def _new_buffer(self, numel: int, dtype) -> _SymmBuffer:
         flat = self._alloc(numel, dtype)

@@ -8,7 +8,7 @@ hook that completes a bucket - the kernel then overlaps the rest of backward - a
 the owner's slice of the fp32 master weights and broadcasts the new bf16 parameters, so
 `optimizer.step()` has nothing left to do for those buckets.
 
-Symmetric memory and the rendezvous come from `torch.distributed._symmetric_memory`
+Symmetric memory comes from a provider in `parallel/symm_memory.py` (torch's, or this library's own heap)
 (plumbing); every byte that crosses NVLink is moved by `bucket_allreduce_kernel`.
 Set `NT_FUSED_ALLREDUCE=0` to keep the NCCL all-reduce (the measured baseline).
 """
@@ -38,9 +38,9 @@ def owned_slice(numel: int, world: int, rank: int) -> tuple[int, int]:
 
 class BucketEngine:
     def __init__(self, group, device: torch.device):
-        import torch.distributed._symmetric_memory as symm_mem
+        from nanotitan_b200.parallel.symm_memory import make_provider
 
-        self.symm_mem = symm_mem
+        self.symm = make_provider(group, device)
         self.group = group
         self.device = device
         self.world = dist.get_world_size(group)
@@ -49,7 +49,6 @@ class BucketEngine:
         self.wait_ms = float(os.environ.get("NT_COMM_WAIT_MS", "60000"))
         self.blocks = int(os.environ.get("NT_ALLREDUCE_BLOCKS", "64"))
         self.stream = torch.cuda.Stream(device=device)
-        self._handles: dict[int, object] = {}
         self.flags = self.alloc(FLAG_WORDS, torch.int32, device)
         self.flags.zero_()
         self.flag_peers = self._peer_table(self.flags)
@@ -64,17 +63,15 @@ class BucketEngine:
     # ------------------------------------------------------------------ memory
     def alloc(self, numel: int, dtype: torch.dtype, device) -> torch.Tensor:
         """Symmetric allocation; every rank of the group must call in the same order."""
-        t = self.symm_mem.empty(numel, dtype=dtype, device=device)
-        self._handles[t.data_ptr()] = self.symm_mem.rendezvous(t, self.group)
-        return t
+        return self.symm.empty(numel, dtype)
 
     def _peer_table(self, t: torch.Tensor) -> torch.Tensor:
-        return torch.tensor(list(self._handles[t.data_ptr()].buffer_ptrs), dtype=torch.int64)
+        return torch.tensor(self.symm.peer_ptrs(t), dtype=torch.int64)
 
     def _multicast(self, t: torch.Tensor) -> int:
         if not self.use_multicast:
             return 0
-        return int(getattr(self._handles[t.data_ptr()], "multicast_ptr", 0) or 0)
+        return self.symm.multicast_ptr(t)
 
     def owned_slice(self, numel: int) -> tuple[int, int]:
         return owned_slice(numel, self.world, self.rank)

@@ -52,10 +52,11 @@ def test_four_gpu_three_d():
     run_distributed(_train_worker, 4, 1, 2, 2, 4, 4, backend="nccl")
 
 
-def _engine_worker(rank, world, multimem):
+def _engine_worker(rank, world, multimem, heap="torch"):
     import os
 
     os.environ["NT_MULTIMEM"] = "1" if multimem else "0"
+    os.environ["NT_SYMM_HEAP"] = heap
     os.environ["NT_COMM_WAIT_MS"] = "3000"
     import torch.distributed as dist
     import torch.nn as nn
@@ -72,6 +73,7 @@ def _engine_worker(rank, world, multimem):
     start = [p.detach().clone() for p in params]
     engine = fused_allreduce.make_engine(dist.group.WORLD, world, dev)
     assert engine is not None, "symmetric memory could not be set up"
+    assert engine.symm.name == heap
     red = ReducerV1(params, world, dist.group.WORLD, bucket_size=1, engine=engine)
 
     def backward(seed):
@@ -141,6 +143,19 @@ def test_fused_bucket_allreduce_and_adamw(multimem, world):
     """World 3 gives ragged slices (bucket lengths are multiples of 128, not of 8 * 3)."""
     _need(world)
     run_distributed(_engine_worker, world, multimem, backend="nccl")
+
+
+@pytest.mark.parametrize("multimem", [False, True])
+def test_native_symmetric_heap(multimem):
+    """The fused all-reduce + AdamW on allocations of this library's own symmetric heap instead of torch's.
+    Runs only when asked for (NT_TEST_NATIVE_HEAP=1): the heap's CUDA driver table has not run on a GPU yet,
+    so it is not part of the default tier."""
+    import os
+
+    if os.environ.get("NT_TEST_NATIVE_HEAP") != "1":
+        pytest.skip("set NT_TEST_NATIVE_HEAP=1 to run the native symmetric heap on GPUs")
+    _need(2)
+    run_distributed(_engine_worker, 2, multimem, "native", backend="nccl")
 
 
 def _ep_compare_worker(rank, world, starve):
