@@ -5,6 +5,7 @@
 
 #include "cuda_check.h"
 #include "kernels/ops.h"
+#include "token_loader.h"
 
 namespace py = pybind11;
 
@@ -59,6 +60,30 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         "Collective allocation -> (byte tensor over this rank's piece, every rank's address, multicast address, id)");
   m.def("symm_heap_free", &nt::symm_heap_free);
   m.def("symm_heap_close", &nt::symm_heap_close);
+  py::class_<nt::TokenWindowLoader>(m, "TokenWindowLoader",
+                                    "Background threads cutting training windows from a uint16 token file into a ring of int64 batches")
+      .def(py::init<const std::string&, int64_t, int64_t, int, int>(), py::arg("path"), py::arg("seq_len"), py::arg("batch"),
+           py::arg("depth"), py::arg("threads"))
+      .def_property_readonly("num_sequences", &nt::TokenWindowLoader::num_sequences)
+      .def_property_readonly("slot_elements", &nt::TokenWindowLoader::slot_elements)
+      .def_property_readonly("batches_in_epoch", &nt::TokenWindowLoader::batches_in_epoch)
+      .def("set_ring",
+           [](nt::TokenWindowLoader& self, const at::Tensor& ring, int64_t depth) {
+             TORCH_CHECK(ring.device().is_cpu() && ring.scalar_type() == at::kLong && ring.is_contiguous() &&
+                             ring.numel() == depth * self.slot_elements(),
+                         "ring must be a contiguous int64 host tensor of depth * slot_elements values");
+             self.set_ring(ring.data_ptr<int64_t>());
+           },
+           "The caller keeps `ring` alive while the loader is in use")
+      .def("start",
+           [](nt::TokenWindowLoader& self, const at::Tensor& order) {
+             TORCH_CHECK(order.device().is_cpu() && order.scalar_type() == at::kLong && order.is_contiguous() && order.dim() == 1,
+                         "order must be a contiguous 1-D int64 host tensor");
+             self.start(order.data_ptr<int64_t>(), order.numel());
+           })
+      .def("next", &nt::TokenWindowLoader::next, py::arg("timeout_ms"), py::call_guard<py::gil_scoped_release>())
+      .def("release", &nt::TokenWindowLoader::release)
+      .def("stop", &nt::TokenWindowLoader::stop, py::call_guard<py::gil_scoped_release>());
   m.def("bounded_wait_probe", &nt::bounded_wait_probe, "Let a bounded device wait run out; returns the number of threads that gave up");
   m.def("read_status", &nt::read_status, py::arg("clear") = true, "[code, kernel, detail, count] of the device status word");
   m.def("status_word_tensor", &nt::status_word_tensor);

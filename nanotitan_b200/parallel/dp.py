@@ -78,22 +78,19 @@ class DataParallel:
     def get_reducers(self) -> dict:
         return {"shared": self.shared_reducer, "expert": self.expert_reducer}
 
-    def prepare_trainloader(self, train_dataset) -> DataLoader:
+    def prepare_trainloader(self, train_dataset):
+        """This rank's shuffled shard of the training set, in batches; packed token files are served by the C++
+        loader (data/native_loader.py), anything else by a torch DataLoader."""
+        from nanotitan_b200.data.native_loader import make_train_loader
+
         sampler = DistributedSampler(
             dataset=train_dataset,
             shuffle=True,
             num_replicas=self.dims.data_world_size,
             rank=self.dims.data_rank,
         )
-        return DataLoader(
-            train_dataset,
-            batch_size=self.cfg.trainer.per_device_batch_size,
-            shuffle=False,
-            sampler=sampler,
-            num_workers=self.cfg.data.num_workers,
-            pin_memory=self.device.type == "cuda",
-            drop_last=True,
-        )
+        return make_train_loader(train_dataset, sampler, self.cfg.trainer.per_device_batch_size, self.device,
+                                 self.cfg.data.num_workers)
 
     def prepare_valloader(self, val_dataset) -> DataLoader:
         sampler = DistributedSampler(

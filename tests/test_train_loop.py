@@ -80,3 +80,34 @@ def _two_rank_worker(rank, world, tmp):
 @pytest.mark.distributed
 def test_two_data_parallel_ranks_train_through_the_entrypoint(tmp_path):
     run_distributed(_two_rank_worker, 2, str(tmp_path))
+
+
+def test_a_packed_token_file_trains_through_the_native_loader(tmp_path, monkeypatch):
+    """Without --synthetic-data the entrypoint reads `data.train_tokens_path`; with the extension built those
+    batches come from the C++ window loader, across an epoch boundary (10 batches per epoch, 14 steps)."""
+    from nanotitan_b200 import metrics, train
+    from nanotitan_b200.data.dataset import write_synthetic_token_file
+    from nanotitan_b200.ops.ext import have_ext
+
+    if not have_ext():
+        pytest.skip("the extension is not built")
+    monkeypatch.chdir(tmp_path)
+    tokens = write_synthetic_token_file(tmp_path / "train.bin", 61, 8 * 40 + 1, seed=1)  # 40 windows of 8 tokens
+    data = {"num_workers": 1, "train_tokens_path": str(tokens), "val_tokens_path": str(tokens)}
+    path = _write_cfg(tmp_path, "file.toml", max_steps=14, data=data)
+    seen = []
+    real = train.DataParallel.prepare_trainloader
+
+    def spy(self, dataset):
+        loader = real(self, dataset)
+        seen.append(type(loader).__name__)
+        return loader
+
+    monkeypatch.setattr(train.DataParallel, "prepare_trainloader", spy)
+    logged = []
+    plain = metrics.MetricsLogger.log
+    monkeypatch.setattr(metrics.MetricsLogger, "log",
+                        lambda self, step, metrics: (logged.append(step), plain(self, step, metrics))[1])
+    train.main([str(path), "--log.level", "WARNING"])
+    assert seen == ["NativeTokenLoader"]
+    assert logged == list(range(14))
