@@ -36,8 +36,8 @@ def sources() -> list[str]:
 
 
 def so_path() -> Path | None:
-    hits = sorted(BUILD_DIR.glob(f"{EXT_NAME}*.so"))
-    return hits[0] if hits else None
+    hits = sorted(BUILD_DIR.glob(f"{EXT_NAME}*.so"), key=lambda p: p.stat().st_mtime)
+    return hits[-1] if hits else None  # the newest, when both build routes have left one
 
 
 def build_extension(verbose: bool = False) -> Path:
