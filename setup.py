@@ -20,6 +20,7 @@ def extension():
     from nanotitan_b200.ops import ext
 
     os.environ["TORCH_CUDA_ARCH_LIST"] = "10.0a"  # the -gencode flag below is the one that counts
+    ext.BUILD_DIR.mkdir(parents=True, exist_ok=True)  # where `build_ext --inplace` puts the module
     sources = [os.path.relpath(s, ROOT) for s in ext.sources()]
     flags = [f for f in ext.NVCC_FLAGS if f not in ("-Xptxas", "-v")]
     return CUDAExtension(
