@@ -4,7 +4,8 @@ The key names, defaults and validators follow the reference schema
 (src/config.py:19-153) so every reference TOML loads unchanged; unknown keys are
 rejected everywhere.  Two optional tables are additions of this framework:
 ``[checkpoint]`` (sharded save / resume) and ``[fault]`` (process-group timeout,
-heartbeat).
+heartbeat), and ``runtime.cuda_graph`` is an added key.  Tables appear below in the
+order a config file usually lists them; every key says what it controls.
 """
 from __future__ import annotations
 
@@ -23,46 +24,81 @@ class _Strict(BaseModel):
     model_config = ConfigDict(extra="forbid", arbitrary_types_allowed=True)
 
 
+# --------------------------------------------------------------------------- [model]
+class TokenEmbeddingConfig(_Strict):
+    """[model.token_embedding]: no keys yet; the table may be present and empty."""
+
+
+class PositionalEmbeddingConfig(_Strict):
+    """[model.positional_embedding]: no keys yet (positions are fixed sinusoids)."""
+
+
+class ModelConfig(_Strict):
+    vocab_size: PositiveInt        # rows of the embedding and of the (untied) unembedding
+    d_model: PositiveInt           # residual width
+    d_head: PositiveInt            # per-head width; n_heads * d_head is the attention width
+    n_heads: PositiveInt
+    n_layers: PositiveInt          # transformer layers, each attention + MoE feed-forward
+    max_seq_len: PositiveInt       # tokens per sample and length of the position table
+    ffn_in: PositiveInt            # hidden width of one expert
+    num_experts: PositiveInt       # experts per layer; 1 = a dense SwiGLU feed-forward
+    top_k: PositiveInt             # experts per token
+    token_embedding: TokenEmbeddingConfig = Field(default_factory=TokenEmbeddingConfig)
+    positional_embedding: PositionalEmbeddingConfig = Field(default_factory=PositionalEmbeddingConfig)
+    moe_backend: str = "torch"     # "torch" (portable modules) or "cuda" (this library's kernels)
+    dtype: DTypeName = "float32"   # parameter / activation dtype
+    moe_router_dtype: DTypeName = "float32"
+    router_alpha: float            # weight of the load-balancing loss
+
+    @model_validator(mode="after")
+    def _even_width(self) -> "ModelConfig":
+        if self.d_model % 2 != 0:
+            raise ValueError("model.d_model must be even when using sinusoidal positional embeddings")
+        return self
+
+
+# --------------------------------------------------------------------------- [trainer] [data] [optim]
+class TrainerConfig(_Strict):
+    device_id: NonNegativeInt          # kept for the reference's files; ranks take LOCAL_RANK
+    eval_every_step: int               # -1: never; 0: validate after every step; n: after every n-th step
+    per_device_batch_size: PositiveInt
+    seed: NonNegativeInt               # the reference insists on seed > 0 (src/config.py:121); 0 is a valid seed here
+
+
 class DataConfig(_Strict):
-    num_workers: PositiveInt
-    train_tokens_path: str
+    num_workers: PositiveInt           # loader threads (packed token files) or DataLoader workers
+    train_tokens_path: str             # flat uint16 token stream
     val_tokens_path: str
 
 
 class OptimizerConfig(_Strict):
-    type: str
+    type: str                          # "adam": AdamW, weight decay 0.1
     lr: float
 
 
-class TokenEmbeddingConfig(_Strict):
-    pass
-
-
-class PositionalEmbeddingConfig(_Strict):
-    pass
-
-
+# --------------------------------------------------------------------------- [runtime]
 class RuntimeConfig(_Strict):
     """Parallel layout of one run (reference: src/config.py:42-57)."""
 
     name: str
-    reducer: str = "v0"  # informational only, never branched on
-    bucket_size: int = 25  # MiB per gradient bucket
-    num_microbatches: int = 1
+    reducer: str = "v0"                # informational only, never branched on
+    bucket_size: int = 25              # MiB per gradient bucket
+    num_microbatches: int = 1          # GPipe microbatches per step
     dp_size: int = 1
     pp_size: int = 1
     ep_size: int = 1
-    num_expert: PositiveInt = 1  # mirrored from model.num_experts by AppConfig
+    num_expert: PositiveInt = 1        # mirrored from model.num_experts by AppConfig
     # Capture the whole optimizer step in a CUDA graph after two ordinary steps (GPU, pp_size 1);
     # the environment variable NT_CUDA_GRAPH=0/1 overrides it.  No counterpart in the reference.
     cuda_graph: bool = True
 
 
+# --------------------------------------------------------------------------- optional tables
 class ProfilerConfig(_Strict):
     enabled: bool = False
-    wait_steps: NonNegativeInt = 2
-    warmup_steps: NonNegativeInt = 2
-    active_steps: NonNegativeInt = 6
+    wait_steps: NonNegativeInt = 2     # idle steps before the warm-up
+    warmup_steps: NonNegativeInt = 2   # traced but discarded
+    active_steps: NonNegativeInt = 6   # recorded
     record_shapes: bool = True
     profile_memory: bool = True
     with_stack: bool = False
@@ -76,60 +112,26 @@ class ProfilerConfig(_Strict):
 
 
 class HardwareConfig(_Strict):
-    peak_flops_tflops_per_gpu: float = 0.0
-
-
-class ModelConfig(_Strict):
-    vocab_size: PositiveInt
-    d_model: PositiveInt
-    d_head: PositiveInt
-    n_heads: PositiveInt
-    n_layers: PositiveInt
-    max_seq_len: PositiveInt
-    ffn_in: PositiveInt
-    num_experts: PositiveInt
-    top_k: PositiveInt
-    token_embedding: TokenEmbeddingConfig = Field(default_factory=TokenEmbeddingConfig)
-    positional_embedding: PositionalEmbeddingConfig = Field(
-        default_factory=PositionalEmbeddingConfig
-    )
-    moe_backend: str = "torch"
-    dtype: DTypeName = "float32"
-    moe_router_dtype: DTypeName = "float32"
-    router_alpha: float
-
-    @model_validator(mode="after")
-    def _even_width(self) -> "ModelConfig":
-        if self.d_model % 2 != 0:
-            raise ValueError(
-                "model.d_model must be even when using sinusoidal positional embeddings"
-            )
-        return self
-
-
-class TrainerConfig(_Strict):
-    device_id: NonNegativeInt
-    eval_every_step: int
-    per_device_batch_size: PositiveInt
-    seed: NonNegativeInt  # the reference insists on seed > 0 (src/config.py:121); 0 is a valid seed here
+    peak_flops_tflops_per_gpu: float = 0.0   # > 0 turns on the MFU metric
 
 
 class CheckpointConfig(_Strict):
     """Sharded checkpointing (no counterpart in the reference, which never saves)."""
 
     dir: str = ""
-    every_steps: NonNegativeInt = 0  # 0 disables periodic saves
+    every_steps: NonNegativeInt = 0    # 0 disables periodic saves
     resume: bool = False
 
 
 class FaultConfig(_Strict):
     """Host-side failure detection (no counterpart in the reference)."""
 
-    pg_timeout_s: float = 600.0
-    heartbeat_dir: str = ""
-    heartbeat_stale_s: float = 120.0
+    pg_timeout_s: float = 600.0        # process-group timeout: ends a collective a lost peer never joins
+    heartbeat_dir: str = ""            # "" disables heartbeats
+    heartbeat_stale_s: float = 120.0   # a peer silent for longer counts as lost
 
 
+# --------------------------------------------------------------------------- the file
 class AppConfig(_Strict):
     run_name: str
     max_steps: PositiveInt
@@ -142,7 +144,7 @@ class AppConfig(_Strict):
     hardware: HardwareConfig = Field(default_factory=HardwareConfig)
     checkpoint: CheckpointConfig = Field(default_factory=CheckpointConfig)
     fault: FaultConfig = Field(default_factory=FaultConfig)
-    track_backward_time: bool = False
+    track_backward_time: bool = False  # accepted for the reference's files; time/backward_time is always reported
 
     @model_validator(mode="before")
     @classmethod

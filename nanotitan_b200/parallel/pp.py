@@ -213,6 +213,38 @@ class PipelineParallel:
             return self._graphed_step(model, batch, optimizer, collect_metrics)
         return self._eager_step(model, batch, optimizer, collect_metrics)
 
+    @torch.no_grad()
+    def eval_step(self, model, batch):
+        """Forward only, through the same microbatches and stage boundaries as a training step: the mean
+        cross-entropy of this rank's batch on the last pipeline stage (a 0-d tensor on the device), None on
+        the other stages.  Nothing is kept for a backward pass.  The reference has the hook for this
+        (`trainer.eval_every_step`, `DataParallel.prepare_valloader`) but its loop is commented out
+        (src/train.py:187-205)."""
+        x, y = batch
+        n_mb = self.cfg.runtime.num_microbatches
+        microbatch_x, microbatch_y = self.prepare_microbatch(x, y)
+        self.microbatch_size = x.shape[0] // n_mb
+        first, last = self.dim.is_pp_first_stage, self.dim.is_pp_last_stage
+        if self.device.type == "cuda" and self.dim.ep_size > 1:
+            from nanotitan_b200.parallel import ep_fused
+
+            ep_fused.reset_pools()  # no backward runs here to hand the staging buffers back
+        self._recv_waits = []
+        losses = []
+        recvs = [] if first else self._post_recvs(self.dim.prev_pp_rank, n_mb)
+        for i, (mb_x, mb_y) in enumerate(zip(microbatch_x, microbatch_y, strict=False)):
+            mb_x = mb_x.to(self.device, non_blocking=True) if first else self._recv(recvs[i], self.dim.prev_pp_rank)
+            out, _ = model(mb_x)
+            if last:
+                mb_y = mb_y.to(self.device, non_blocking=True)
+                losses.append(torch.nn.functional.cross_entropy(out.reshape(-1, out.size(-1)).float(), mb_y.reshape(-1)))
+            else:
+                self._send(out, self.dim.next_pp_rank)
+        for _, work in self._pending:
+            work.wait()
+        self._pending = []
+        return torch.stack(losses).mean() if last else None
+
     def _eager_step(self, model, batch, optimizer, collect_metrics):
         x, y = batch
         n_mb = self.cfg.runtime.num_microbatches

@@ -41,6 +41,8 @@ def parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--resume", default="", help="Checkpoint directory to resume from.")
     parser.add_argument("--synthetic-data", action="store_true",
                         help="Uniform-random token ids instead of the token file.")
+    parser.add_argument("--eval-batches", type=int, default=20,
+                        help="Validation batches per rank and evaluation (trainer.eval_every_step != -1).")
     parser.add_argument("config", help="TOML config path, optionally prefixed with '@'.")
     return parser.parse_args(argv)
 
@@ -93,6 +95,14 @@ def main(argv=None) -> None:
     else:
         train_dataset = PackedTokenDataset(cfg.data.train_tokens_path, cfg.model.max_seq_len)
     train_loader = dp.prepare_trainloader(train_dataset)
+    val_loader = None
+    if cfg.trainer.eval_every_step != -1:
+        if args.synthetic_data:
+            n_val = cfg.trainer.per_device_batch_size * dims.data_world_size * args.eval_batches
+            val_dataset = SyntheticTokenDataset(cfg.model.vocab_size, cfg.model.max_seq_len, n_val, cfg.trainer.seed + 1)
+        else:
+            val_dataset = PackedTokenDataset(cfg.data.val_tokens_path, cfg.model.max_seq_len)
+        val_loader = dp.prepare_valloader(val_dataset)
 
     counts = torch.tensor(
         [model.total_parameter_count(), float(model.active_parameter_count())],
@@ -160,6 +170,23 @@ def main(argv=None) -> None:
                         metrics["train/tokens_per_second"], 1e3 * metrics["time/step_time"])
             metrics_logger.log(step=index, metrics=metrics)
 
+    def evaluate(index: int) -> None:
+        """Mean validation cross-entropy over at most `--eval-batches` full batches per rank, logged as
+        `val/ce_loss` at step `index`.  Every rank runs the same number of batches (the sampler pads the
+        shards to equal length), so the collectives inside the model line up."""
+        total = torch.zeros(2, dtype=torch.float64, device=device)  # [sum of batch means, batches]
+        for n, batch in enumerate(val_loader):
+            if n >= args.eval_batches or batch[0].shape[0] != cfg.trainer.per_device_batch_size:
+                break
+            loss = pp.eval_step(model, batch)
+            if loss is not None:
+                total += torch.stack([loss.double(), torch.ones((), dtype=torch.float64, device=device)])
+        reduce_scalars(total, None)  # over all ranks; only last pipeline stages contributed
+        if total[1] > 0 and dims.local_rank == 0:
+            value = float(total[0] / total[1])
+            logger.info("step %d | val ce %.4f over %d batches", index, value, int(total[1]))
+            metrics_logger.log(step=index, metrics={"val/ce_loss": value})
+
     logger.info("Attempting to begin training")
     try:
         epoch = 0
@@ -188,6 +215,11 @@ def main(argv=None) -> None:
                     prof.step()
                     if heartbeat is not None:
                         heartbeat.beat(step)
+                    # -1: never, 0: after every step, n: after every n-th step (the rule of the reference's
+                    # commented-out loop, src/train.py:187-190)
+                    every_eval = cfg.trainer.eval_every_step
+                    if val_loader is not None and (every_eval == 0 or step % every_eval == 0):
+                        evaluate(step - 1)
                     every = cfg.checkpoint.every_steps
                     if cfg.checkpoint.dir and every and step % every == 0:
                         check_peers()

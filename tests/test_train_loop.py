@@ -111,3 +111,43 @@ def test_a_packed_token_file_trains_through_the_native_loader(tmp_path, monkeypa
     train.main([str(path), "--log.level", "WARNING"])
     assert seen == ["NativeTokenLoader"]
     assert logged == list(range(14))
+
+
+def test_validation_loss_is_logged_on_the_configured_steps(tmp_path, monkeypatch):
+    monkeypatch.chdir(tmp_path)
+    cfg = tiny_app_cfg().model_dump(mode="json")
+    cfg["max_steps"] = 5
+    cfg["trainer"]["eval_every_step"] = 2
+    from nanotitan_b200.sweep import dump_toml
+
+    path = tmp_path / "eval.toml"
+    path.write_text(dump_toml(cfg), encoding="utf-8")
+    logged = []
+    _run_main(path, logged, extra=("--eval-batches", "3"))
+    val = [(s, m["val/ce_loss"]) for s, m in logged if "val/ce_loss" in m]
+    assert [s for s, _ in val] == [1, 3]  # after the second and the fourth step
+    assert all(0.0 < v < 10.0 for _, v in val)
+    assert [s for s, m in logged if "train/ce_loss" in m] == [0, 1, 2, 3, 4]
+
+
+def _pipeline_eval_worker(rank, world, tmp):
+    import os
+
+    os.chdir(tmp)
+    cfg = tiny_app_cfg(pp=2, microbatches=2).model_dump(mode="json")
+    cfg["max_steps"] = 2
+    cfg["trainer"]["eval_every_step"] = 0  # after every step
+    from nanotitan_b200.sweep import dump_toml
+
+    path = Path(tmp) / f"pp{rank}.toml"
+    path.write_text(dump_toml(cfg), encoding="utf-8")
+    logged = []
+    _run_main(path, logged, extra=("--eval-batches", "2"))
+    if rank == 0:
+        val = [(s, m["val/ce_loss"]) for s, m in logged if "val/ce_loss" in m]
+        assert [s for s, _ in val] == [0, 1] and all(0.0 < v < 10.0 for _, v in val), val
+
+
+@pytest.mark.distributed
+def test_validation_runs_through_the_pipeline_stages(tmp_path):
+    run_distributed(_pipeline_eval_worker, 2, str(tmp_path))
