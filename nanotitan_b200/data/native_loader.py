@@ -35,12 +35,14 @@ class NativeTokenLoader:
         self._ring = torch.empty(depth * int(self._loader.slot_elements), dtype=torch.int64, pin_memory=self.on_gpu)
         self._loader.set_ring(self._ring, depth)
         self._slots = self._ring.view(depth, 2, batch_size, seq_len)
+        self.skip_batches = 0  # the next epoch starts this many batches in (a resumed run); then back to 0
 
     def __len__(self) -> int:
         return len(self.sampler) // self.batch_size
 
     def __iter__(self):
         order = torch.tensor(list(iter(self.sampler)), dtype=torch.int64)
+        order, self.skip_batches = order[self.skip_batches * self.batch_size :].contiguous(), 0
         self._loader.start(order)
         held: deque[tuple[int, object]] = deque()  # (slot, event that covers the consumer's use of it)
         try:
@@ -63,6 +65,19 @@ class NativeTokenLoader:
                 yield (x, y) if self.on_gpu else (x.clone(), y.clone())
         finally:
             self._loader.stop()
+
+
+def skip_batches(loader, n: int):
+    """Iterator over `loader`'s next epoch without its first `n` batches.  The native loader never builds
+    them; a torch DataLoader has to produce and drop them."""
+    if n and isinstance(loader, NativeTokenLoader):
+        loader.skip_batches = n
+        return iter(loader)
+    it = iter(loader)
+    for _ in range(n):
+        if next(it, None) is None:
+            break
+    return it
 
 
 def make_train_loader(dataset, sampler, batch_size: int, device: torch.device, num_workers: int):

@@ -1,10 +1,10 @@
 """Process-group bootstrap helpers.
 
-Same surface as the reference (src/dist_env.py:7-48) with three differences: the
+Same surface as the reference (src/dist_env.py:7-48) with four differences: the
 backend is NCCL when CUDA is present and gloo otherwise, a single process also gets
 a (size-1) group so the rank-layout code never special-cases it, and every group
 carries a finite timeout so a lost peer ends a collective with an error instead of
-a hang.
+a hang; and ranks restarted by the launcher rendezvous under a store prefix of their attempt.
 """
 from __future__ import annotations
 
@@ -37,6 +37,15 @@ def init_distributed(timeout_s: float = 600.0, backend: str | None = None) -> No
     kwargs = {}
     if backend == "nccl":
         kwargs["device_id"] = torch.device("cuda", local_rank)
+    restart = int(os.environ.get("TORCHELASTIC_RESTART_COUNT", "0"))
+    if restart > 0 and os.environ.get("TORCHELASTIC_USE_AGENT_STORE") == str(True):
+        # A launcher restart (torchrun --max-restarts) reuses the agent's store, which still holds the
+        # rendezvous keys of the attempt that died: the new ranks would read the dead ranks' addresses from
+        # it and wait for them.  Every attempt after the first therefore works under a prefix of its own.
+        store = dist.TCPStore(os.environ["MASTER_ADDR"], int(os.environ["MASTER_PORT"]), world, is_master=False, timeout=timeout)
+        dist.init_process_group(backend=backend, store=dist.PrefixStore(f"nt_attempt_{restart}/", store),
+                                rank=int(os.environ["RANK"]), world_size=world, timeout=timeout, **kwargs)
+        return
     dist.init_process_group(backend=backend, init_method="env://", timeout=timeout, **kwargs)
 
 

@@ -11,10 +11,12 @@ from __future__ import annotations
 
 import argparse
 import logging
+import os
 
 import torch
 
 from nanotitan_b200.data.dataset import PackedTokenDataset, SyntheticTokenDataset
+from nanotitan_b200.data.native_loader import skip_batches
 from nanotitan_b200.dist_env import barrier, cleanup, get_world_size, init_distributed, local_device
 from nanotitan_b200.metrics import MetricsLogger, ScalarMetric, reduce_metrics
 from nanotitan_b200.models.model import NanoTitanModel
@@ -117,12 +119,15 @@ def main(argv=None) -> None:
 
     step = 0
     tokens_seen = 0
+    epoch, batches_done = 0, 0  # loader position: batches of `epoch` already taken
     resume_dir = args.resume or (cfg.checkpoint.dir if cfg.checkpoint.resume else "")
     if resume_dir:
         found = latest_checkpoint(resume_dir)
         if found is not None:
             state = load_checkpoint(found, model, optimizer, dims)
             step, tokens_seen = state["step"], state["tokens_seen"]
+            if state.get("data"):
+                epoch, batches_done = state["data"]["epoch"], state["data"]["batches_done"]
             logger.info("resumed from %s at step %d", found, step)
 
     heartbeat = Heartbeat(cfg.fault.heartbeat_dir, dims.global_rank) if cfg.fault.heartbeat_dir else None
@@ -135,6 +140,24 @@ def main(argv=None) -> None:
         (instead of after an in-kernel wait or a process-group timeout runs out)."""
         if heartbeat is not None:
             assert_peers_alive(cfg.fault.heartbeat_dir, world_size, cfg.fault.heartbeat_stale_s)
+
+    inject = os.environ.get("NT_INJECT_EXIT", "")
+
+    def inject_exit(at_step: int) -> None:
+        """Host-side fault injection for restart tests: `NT_INJECT_EXIT=rank:step[:attempt]` makes that rank
+        leave the job right before it would launch `step`, on the given launcher attempt (default: the first).
+        The rank leaves between steps with nothing of its own in flight."""
+        if not inject:
+            return
+        rank_s, step_s, *rest = inject.split(":")
+        attempt = int(rest[0]) if rest else 0
+        if (int(rank_s), int(step_s), attempt) != (dims.global_rank, at_step, int(os.environ.get("TORCHELASTIC_RESTART_COUNT", "0"))):
+            return
+        if device.type == "cuda":
+            torch.cuda.synchronize(device)
+        logger.error("NT_INJECT_EXIT: rank %d leaves before step %d", dims.global_rank, at_step)
+        logging.shutdown()
+        os._exit(17)
 
     profiler = build_profiler(cfg.run_name, cfg.profiler, dims)
     flops_per_token = model_flops_per_token(cfg, active_params)
@@ -188,8 +211,10 @@ def main(argv=None) -> None:
             metrics_logger.log(step=index, metrics={"val/ce_loss": value})
 
     logger.info("Attempting to begin training")
+    def data_state() -> dict:
+        return {"epoch": epoch, "batches_done": batches_done}
+
     try:
-        epoch = 0
         # On GPUs the loop runs one step ahead of its own reporting: step i+1 is launched before the metrics
         # of step i are collected, so reading the losses never leaves the device idle.  On CPU a step's
         # collectives block the host, there is nothing to overlap, and every step is reported at once.
@@ -199,12 +224,14 @@ def main(argv=None) -> None:
             while step < cfg.max_steps:
                 if hasattr(train_loader.sampler, "set_epoch"):
                     train_loader.sampler.set_epoch(epoch)
-                progressed = False
-                for batch in train_loader:
+                progressed = batches_done > 0
+                for batch in skip_batches(train_loader, batches_done):
                     progressed = True
                     check_peers()
+                    inject_exit(step)
                     pending = pp.train_step(model, batch, optimizer, collect_metrics="deferred")
                     tokens_seen += tokens_per_step
+                    batches_done += 1
                     if in_flight is not None:
                         report(in_flight)
                     in_flight = (step, tokens_seen, pending)
@@ -223,10 +250,11 @@ def main(argv=None) -> None:
                     every = cfg.checkpoint.every_steps
                     if cfg.checkpoint.dir and every and step % every == 0:
                         check_peers()
-                        save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg)
+                        save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg, data_state())
                     if step >= cfg.max_steps:
                         break
-                epoch += 1
+                else:  # the epoch ran out (no break): the next one starts from its first batch
+                    epoch, batches_done = epoch + 1, 0
                 if not progressed:
                     raise RuntimeError("the training loader produced no batch (dataset too small)")
             if in_flight is not None:
@@ -234,7 +262,7 @@ def main(argv=None) -> None:
                 in_flight = None
         if cfg.checkpoint.dir:
             check_peers()
-            save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg)
+            save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg, data_state())
     finally:
         if heartbeat is not None:
             heartbeat.leave(step)

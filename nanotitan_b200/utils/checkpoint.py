@@ -3,7 +3,8 @@
 The reference never saves anything; the layout to honour is its `state_dict()` key
 scheme (stage-local `blocks.<i>` indices, local expert slices).  A shard file holds
 that state dict (tensors cloned out of the flat buckets they view into), the
-optimizer state, step, token count, RNG states and the rank's coordinates.
+optimizer state, step, token count, the loader position (epoch and batches taken from it),
+RNG states and the rank's coordinates.
 `consolidate` rebuilds the single-process view (global layer indices, all experts)
 so weights can be exchanged with a reference run.
 """
@@ -23,7 +24,9 @@ def _rank_file(step_dir: Path, rank: int) -> Path:
     return step_dir / f"rank_{rank:05d}.pt"
 
 
-def save_checkpoint(directory, step: int, tokens_seen: int, model, optimizer, dims, cfg=None) -> Path:
+def save_checkpoint(directory, step: int, tokens_seen: int, model, optimizer, dims, cfg=None, data_state=None) -> Path:
+    """`data_state` is the loader position ({"epoch", "batches_done"}): a resumed run continues with the batch
+    the interrupted one would have taken next."""
     step_dir = Path(directory) / f"step_{step:08d}"
     step_dir.mkdir(parents=True, exist_ok=True)
     payload = {
@@ -31,6 +34,7 @@ def save_checkpoint(directory, step: int, tokens_seen: int, model, optimizer, di
         "optimizer": optimizer.state_dict() if optimizer is not None else None,
         "step": step,
         "tokens_seen": tokens_seen,
+        "data": dict(data_state) if data_state else None,
         "rng": {
             "torch": torch.get_rng_state(),
             "cuda": torch.cuda.get_rng_state_all() if torch.cuda.is_available() else None,
@@ -114,7 +118,7 @@ def load_checkpoint(step_dir, model, optimizer, dims) -> dict:
     torch.set_rng_state(payload["rng"]["torch"])
     if payload["rng"]["cuda"] is not None and torch.cuda.is_available():
         torch.cuda.set_rng_state_all(payload["rng"]["cuda"])
-    return {"step": payload["step"], "tokens_seen": payload["tokens_seen"]}
+    return {"step": payload["step"], "tokens_seen": payload["tokens_seen"], "data": payload.get("data")}
 
 
 def consolidate(step_dir) -> dict[str, torch.Tensor]:

@@ -13,6 +13,8 @@ import torch
 from tests.conftest import run_distributed
 from tests.helpers import fake_dims, full_spec, random_batch, tiny_app_cfg
 
+ROOT = Path(__file__).resolve().parent.parent
+
 
 # ------------------------------------------------------------------ heartbeat
 def test_heartbeat_marks_stale_and_missing_ranks(tmp_path):
@@ -234,3 +236,48 @@ def test_cross_rank_barrier_wait_runs_out_on_one_gpu():
     ext.copy_vector(torch.arange(8, dtype=torch.float32, device=dev), y)
     assert y.tolist() == list(range(8))
     assert ext.read_status(True)[0] == 0
+
+
+# ------------------------------------------------------------------ restart by the launcher
+def _launch(tmp_path, name, ckpt_dir, env_extra, restarts):
+    import os
+    import socket
+    import subprocess
+    import sys
+
+    from nanotitan_b200.sweep import dump_toml
+
+    cfg = tiny_app_cfg(dp=2, batch=2).model_dump(mode="json")
+    cfg.update(max_steps=6, run_name=name, checkpoint={"dir": str(ckpt_dir), "every_steps": 2, "resume": True})
+    path = tmp_path / f"{name}.toml"
+    path.write_text(dump_toml(cfg), encoding="utf-8")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=str(ROOT), **env_extra)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--max-restarts", str(restarts),
+           "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "nanotitan_b200.train", str(path),
+           "--synthetic-data", "--log.level", "INFO"]
+    return subprocess.run(cmd, cwd=tmp_path, env=env, capture_output=True, text=True, timeout=240)
+
+
+@pytest.mark.distributed
+def test_launcher_restart_resumes_from_the_last_checkpoint_and_ends_where_a_clean_run_ends(tmp_path):
+    """Rank 1 leaves the job before step 3 of the first attempt (host-side injection).  The launcher restarts
+    both ranks; they resume from the step-2 checkpoint - weights, optimizer, RNG and loader position - and the
+    final weights are bitwise those of a run that was never interrupted."""
+    from nanotitan_b200.utils.checkpoint import consolidate, latest_checkpoint
+
+    clean = _launch(tmp_path, "clean", tmp_path / "ckpt_clean", {}, restarts=0)
+    assert clean.returncode == 0, clean.stderr[-3000:]
+    broken = _launch(tmp_path, "broken", tmp_path / "ckpt_broken", {"NT_INJECT_EXIT": "1:3:0"}, restarts=1)
+    assert broken.returncode == 0, broken.stderr[-3000:]
+    log = broken.stdout + broken.stderr
+    assert "NT_INJECT_EXIT: rank 1 leaves before step 3" in log
+    assert "resumed from" in log and "at step 2" in log
+    a, b = latest_checkpoint(tmp_path / "ckpt_clean"), latest_checkpoint(tmp_path / "ckpt_broken")
+    assert a.name == b.name == "step_00000006"
+    wa, wb = consolidate(a), consolidate(b)
+    assert wa.keys() == wb.keys()
+    for key in wa:
+        assert torch.equal(wa[key], wb[key]), key

@@ -67,3 +67,23 @@ def test_leaving_an_epoch_early_and_starting_over(tmp_path):
     assert len(again) == 20 and torch.equal(first[0], again[0][0])
     assert torch.equal(again[5][0][1], torch.from_numpy(dataset.tokens[11 * 8 : 12 * 8].astype("int64")))
     assert torch.equal(again[5][1][1], torch.from_numpy(dataset.tokens[11 * 8 + 1 : 12 * 8 + 1].astype("int64")))
+
+
+@needs_ext
+def test_a_resumed_epoch_starts_where_the_interrupted_one_stopped(tmp_path):
+    from nanotitan_b200.data.native_loader import make_train_loader, skip_batches
+
+    path = write_synthetic_token_file(tmp_path / "tokens.bin", 1000, 8 * 30 + 1, seed=5)
+    dataset = PackedTokenDataset(path, 8)
+    for loader in (make_train_loader(dataset, DistributedSampler(dataset, num_replicas=1, rank=0, shuffle=True, seed=1), 4,
+                                     torch.device("cpu"), num_workers=1),
+                   DataLoader(dataset, batch_size=4, drop_last=True,
+                              sampler=DistributedSampler(dataset, num_replicas=1, rank=0, shuffle=True, seed=1))):
+        loader.sampler.set_epoch(2)
+        whole = list(loader)
+        rest = list(skip_batches(loader, 3))
+        assert len(whole) == 7 and len(rest) == 4
+        for (ax, ay), (bx, by) in zip(whole[3:], rest):
+            assert torch.equal(ax, bx) and torch.equal(ay, by)
+        assert len(list(loader)) == 7  # the skip applies to one epoch only
+        assert list(skip_batches(loader, 7)) == [] and list(skip_batches(loader, 9)) == []
