@@ -181,3 +181,29 @@ def load_full_state(model, full_state: dict[str, torch.Tensor]) -> None:
     with torch.no_grad():
         for key, value in shard_from_full(full_state, model.spec).items():
             own[key].copy_(value)
+
+
+def main(argv=None) -> int:
+    """`python -m nanotitan_b200.utils.checkpoint consolidate <checkpoint dir or step dir> <out.pt>`: write the
+    single-process state dict (the reference's key layout) of a sharded checkpoint, e.g. to load it into the
+    reference's model, or with `load_full_state` into a run of another pp x ep layout."""
+    import argparse
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    sub = ap.add_subparsers(dest="command", required=True)
+    cons = sub.add_parser("consolidate", help="merge the rank shards into one state dict")
+    cons.add_argument("checkpoint", help="a step_* folder, or the folder holding them (newest complete one is taken)")
+    cons.add_argument("out", help="file to write (torch.save of {key: tensor})")
+    args = ap.parse_args(argv)
+    found = latest_checkpoint(args.checkpoint)
+    if found is None:
+        raise SystemExit(f"no complete checkpoint under {args.checkpoint}")
+    state = consolidate(found)
+    torch.save(state, args.out)
+    n = sum(v.numel() for v in state.values())
+    print(f"{found}: {len(state)} tensors, {n / 1e6:.2f} M values -> {args.out}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -63,6 +63,20 @@ def test_a_run_resumes_from_its_own_checkpoint(tmp_path, monkeypatch):
     assert [s for s, _ in more] == [2, 3]
     assert more[0][1]["train/total_tokens_seen"] == 3 * logged[0][1]["train/tokens_per_step"]
 
+    # the command-line consolidation of that checkpoint loads into the reference-layout model
+    import torch
+
+    from nanotitan_b200.models import ModelShardSpec, NanoTitanModel
+    from nanotitan_b200.utils import checkpoint
+
+    out = tmp_path / "full.pt"
+    assert checkpoint.main(["consolidate", str(tmp_path / "ckpt"), str(out)]) == 0
+    state = torch.load(out)
+    cfg = tiny_app_cfg().model
+    model = NanoTitanModel(cfg, ModelShardSpec.full(cfg))
+    assert list(state) == list(model.state_dict())
+    model.load_state_dict(state)
+
 
 def _two_rank_worker(rank, world, tmp):
     import os
