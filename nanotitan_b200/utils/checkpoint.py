@@ -130,6 +130,7 @@ def consolidate(step_dir) -> dict[str, torch.Tensor]:
     shards = [s for s in shards if s["coords"]["dp_rank"] == 0]
     merged: dict[str, torch.Tensor] = {}
     expert_parts: dict[str, dict[int, torch.Tensor]] = {}
+    seen: list[str] = []  # keys in the order a model lists them within a block
     for s in shards:
         shift = (s["spec"]["layer_start"] + 1) - (1 if s["spec"]["has_token_embed"] else 0)
         for key, value in s["model"].items():
@@ -139,13 +140,17 @@ def consolidate(step_dir) -> dict[str, torch.Tensor]:
                 new_key = f"blocks.0.{rest}"
             else:
                 new_key = f"blocks.{local + shift}.{rest}"
+            if new_key not in merged and new_key not in expert_parts:
+                seen.append(new_key)
             if ".ffn.experts." in new_key:
                 expert_parts.setdefault(new_key, {})[s["coords"]["ep_rank"]] = value
             elif s["coords"]["ep_rank"] == 0:
                 merged[new_key] = value
     for key, parts in expert_parts.items():
         merged[key] = torch.cat([parts[r] for r in sorted(parts)], dim=0)
-    return merged
+    # blocks in ascending order, keys of a block in the model's own order: the order of `state_dict()`
+    ordered = sorted(range(len(seen)), key=lambda i: (int(seen[i].split(".")[1]), i))
+    return {seen[i]: merged[seen[i]] for i in ordered if seen[i] in merged}
 
 
 def shard_from_full(full_state: dict[str, torch.Tensor], spec) -> dict[str, torch.Tensor]:
