@@ -16,14 +16,23 @@ from nanotitan_b200.data.dataset import write_synthetic_token_file
 OUT_DIR = Path("data/preprocessed")
 
 
+def write_token_file(token_ids, path) -> None:
+    """Token ids as the flat little-endian uint16 stream the datasets read (src/data/prepare_dataset.py:9-12)."""
+    stream = np.asarray(token_ids, dtype=np.int64)
+    if stream.size and (stream.min() < 0 or stream.max() > 65535):
+        raise ValueError("token ids do not fit in uint16")
+    path = Path(path)
+    path.parent.mkdir(parents=True, exist_ok=True)
+    stream.astype("<u2").tofile(path)
+
+
 def tokenize_split(split: str, tokenizer, out_path: Path) -> int:
     from datasets import load_dataset
 
     ds = load_dataset("roneneldan/TinyStories", split=split)
     chunks = [np.asarray(tokenizer.encode(row["text"]), dtype=np.uint16) for row in ds]
     stream = np.concatenate(chunks) if chunks else np.zeros(0, dtype=np.uint16)
-    out_path.parent.mkdir(parents=True, exist_ok=True)
-    stream.tofile(out_path)
+    write_token_file(stream, out_path)
     return int(stream.size)
 
 

@@ -34,3 +34,36 @@ def grouped_gemm_fn(X, weight, expert_offset):
 
 def torch_backend_all_to_all(x, input_splits, output_splits, group):
     return _moe.all_to_all_rows(x, input_splits, output_splits, group)
+
+
+class _ApplyOnly:
+    """The reference spells these operations as `torch.autograd.Function` subclasses and callers may reach
+    them as `Name.apply(...)` (src/model/moe_ops.py:40-160).  Here the autograd nodes live with the kernels
+    (ops/native.py, ops/moe.py); these names keep that spelling working."""
+
+    def __init__(self):
+        raise TypeError(f"{type(self).__name__} is used through {type(self).__name__}.apply(...)")
+
+
+class PackTokensFN(_ApplyOnly):
+    @staticmethod
+    def apply(X, topk_weights, topk_experts, expert_offset_cpy):
+        return pack_tokens_fn(X, topk_weights, topk_experts, expert_offset_cpy)
+
+
+class CombineTokensFN(_ApplyOnly):
+    @staticmethod
+    def apply(packed_expert_outputs, packed_tokenId, packed_topk_weights, num_tokens, hidden_dim):
+        return combine_tokens_fn(packed_expert_outputs, packed_tokenId, packed_topk_weights, num_tokens, hidden_dim)
+
+
+class GroupedGEMM_FN(_ApplyOnly):
+    @staticmethod
+    def apply(X, expert_offset, weight):  # note the order: offsets before weights, unlike grouped_gemm_fn
+        return grouped_gemm_fn(X, weight, expert_offset)
+
+
+class TorchBackendAll2ALL(_ApplyOnly):
+    @staticmethod
+    def apply(x, input_splits, output_splits, group):
+        return torch_backend_all_to_all(x, input_splits, output_splits, group)

@@ -71,8 +71,8 @@ def seed_everything(seed: int) -> None:
         pass
 
 
-def reduce_scalars(values: torch.Tensor, group) -> None:
-    """In-place SUM over `group` (parameter counts over the pipeline stages); a no-op without a
+def reduce_scalars(scalar_tensor: torch.Tensor, pp_group) -> None:
+    """In-place SUM over `pp_group` (parameter counts over the pipeline stages); a no-op without a
     process group."""
     if dist.is_available() and dist.is_initialized():
-        dist.all_reduce(values, op=dist.ReduceOp.SUM, group=group)
+        dist.all_reduce(scalar_tensor, op=dist.ReduceOp.SUM, group=pp_group)

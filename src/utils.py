@@ -22,5 +22,6 @@ def resolve_device(device_id: int) -> torch.device:
     return torch.device("cuda", device_id) if torch.cuda.is_available() else torch.device("cpu")
 
 
-def get_profiler_trace_dir(run_name: str, log_root: str = "runs") -> Path:
-    return Path(log_root) / run_name / "profiler"
+def get_profiler_trace_dir(run_name: str | None = None, log_root: str = "runs") -> Path | None:
+    """`runs/<run_name>/profiler`; None without a run name (the reference's "no log directory" answer)."""
+    return None if run_name is None else Path(log_root) / run_name / "profiler"
