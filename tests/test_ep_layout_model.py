@@ -67,7 +67,6 @@ def test_every_row_has_one_place_and_comes_back(tokens, k, experts, ep, skew):
     rng = np.random.default_rng(tokens + experts + ep)
     e_loc_n, A = experts // ep, tokens * k
     plans = [_plan(_routing(rng, tokens, k, experts, skew), experts) for _ in range(ep)]
-    idx = None  # the ids themselves are no longer needed: counts and slots carry the layout
     cmat = np.stack([p[0] for p in plans])
     expected = [int(cmat[:, r * e_loc_n : (r + 1) * e_loc_n].sum()) for r in range(ep)]
     capacity = ep * A  # the default: worst case
@@ -113,4 +112,3 @@ def test_every_row_has_one_place_and_comes_back(tokens, k, experts, ep, skew):
             rot = min(start[first * e_loc_n if direction == 0 else first], rows)
             visited = sorted((r0 + rot) - rows if r0 + rot >= rows else r0 + rot for r0 in range(rows))
             assert visited == list(range(rows))
-    assert idx is None
