@@ -57,7 +57,7 @@ def reference_layer(args, rank, world, dev):
     if world > 1:
         dist.broadcast(router.data, src=0)
     torch.manual_seed(10 + rank)
-    w_gate, w_val, w_out = (torch.nn.Parameter((torch.randn(*shape, device=dev) * 0.02).bfloat16())
+    w_gate, w_val, w_out = (torch.nn.Parameter((torch.randn(*shape, device=dev) * 0.02).to(getattr(torch, args.dtype)))
                             for shape in ((E_loc, d, f), (E_loc, d, f), (E_loc, f, d)))
     params = [router, w_gate, w_val, w_out]
 
@@ -103,18 +103,41 @@ def reference_layer(args, rank, world, dev):
     return step, params
 
 
-def main():
-    ap = argparse.ArgumentParser()
+def parse_args(argv=None):
+    """This benchmark's options, plus the spellings of the reference's benchmarks/bench_moe.py:51-61
+    (`--batch` x `--seq-len` tokens, `--d-model`, `--ffn-in`, `--num-experts`, `--backend`, `--dtype`, `--device`)."""
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--tokens", type=int, default=32768)
-    ap.add_argument("--hidden", type=int, default=512)
-    ap.add_argument("--ffn", type=int, default=2048)
-    ap.add_argument("--experts", type=int, default=64)
+    ap.add_argument("--batch", type=int, default=0, help="with --seq-len: tokens = batch x seq-len")
+    ap.add_argument("--seq-len", type=int, default=0)
+    ap.add_argument("--hidden", "--d-model", dest="hidden", type=int, default=512)
+    ap.add_argument("--ffn", "--ffn-in", dest="ffn", type=int, default=2048)
+    ap.add_argument("--experts", "--num-experts", dest="experts", type=int, default=64)
     ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--ep", type=int, default=1)
     ap.add_argument("--exchange", choices=["p2p", "nccl"], default="p2p")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    args = ap.parse_args()
+    ap.add_argument("--backend", choices=["cuda", "torch"], default="cuda",
+                    help="ours: the sm_100a kernels, or the portable torch modules (single rank)")
+    ap.add_argument("--dtype", choices=["float16", "bfloat16"], default="bfloat16")
+    ap.add_argument("--device", type=int, default=None, help="single-rank runs: CUDA device index")
+    args = ap.parse_args(argv)
+    if args.batch or args.seq_len:
+        if not (args.batch and args.seq_len):
+            ap.error("--batch and --seq-len go together")
+        args.tokens = args.batch * args.seq_len
+    if args.experts % args.ep:
+        ap.error("--experts must be a multiple of --ep")
+    if args.backend == "torch" and args.ep > 1 and args.impl == "ours":
+        ap.error("--backend torch is a single-rank comparison")
+    return args
+
+
+def main(argv=None):
+    args = parse_args(argv)
+    if args.device is not None and args.ep == 1:
+        torch.cuda.set_device(args.device)
     if args.exchange == "nccl":
         os.environ["NT_FUSED_EP"] = "0"
     rank, world = 0, 1
@@ -126,7 +149,7 @@ def main():
         assert world == args.ep
     dev = torch.device("cuda", torch.cuda.current_device())
     torch.manual_seed(1 + rank)
-    x = torch.randn(1, args.tokens, args.hidden, device=dev).bfloat16().requires_grad_()
+    x = torch.randn(1, args.tokens, args.hidden, device=dev).to(getattr(torch, args.dtype)).requires_grad_()
     g = torch.randn_like(x)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     if args.impl == "reference":
@@ -146,7 +169,7 @@ def main():
     from nanotitan_b200.models.utils import ModelShardSpec
 
     cfg = ModelConfig(vocab_size=8, d_model=args.hidden, d_head=32, n_heads=1, n_layers=1, max_seq_len=8, ffn_in=args.ffn,
-                      num_experts=args.experts, top_k=args.top_k, router_alpha=0.01, moe_backend="cuda", dtype="bfloat16")
+                      num_experts=args.experts, top_k=args.top_k, router_alpha=0.01, moe_backend=args.backend, dtype=args.dtype)
     per = args.experts // world
     spec = ModelShardSpec(0, 1, False, False, False, per, rank * per, (rank + 1) * per, ep_size=world,
                           ep_group=dist.group.WORLD if world > 1 else None)
@@ -166,7 +189,7 @@ def main():
         out, _ = moe(x)
         out.backward(g)
 
-    label = "sm_100a kernels" + ((" + fused peer-store exchange" if args.exchange == "p2p" else " + NCCL all_to_all") if world > 1 else "")
+    label = ("sm_100a kernels" if args.backend == "cuda" else "torch modules") + ((" + fused peer-store exchange" if args.exchange == "p2p" else " + NCCL all_to_all") if world > 1 else "")
     report(args, time_steps(step, args.iters, flush, world, dev), rank, world, label)
 
 

@@ -48,3 +48,15 @@ def test_ncu_launcher_command(capsys):
     assert "regex:.*pack_fwd_kernel.*" in line
     assert "profiles/raw/pack_tokens/pack_T4096_d1024_k2_E16_bf16" in line
     assert "bench_pack_tokens.py" in line and "--tokens 4096" in line and "--warmup 3" in line
+
+
+def test_moe_benchmark_accepts_its_own_and_the_reference_spellings():
+    from benchmarks import bench_moe as b
+
+    args = b.parse_args([])
+    assert (args.tokens, args.hidden, args.ffn, args.experts, args.top_k, args.backend, args.dtype) == \
+        (32768, 512, 2048, 64, 8, "cuda", "bfloat16")
+    args = b.parse_args(["--batch", "8", "--seq-len", "1024", "--d-model", "1024", "--ffn-in", "4096", "--num-experts", "16",
+                         "--top-k", "2", "--backend", "torch", "--dtype", "float16", "--device", "0"])
+    assert (args.tokens, args.hidden, args.ffn, args.experts, args.top_k, args.backend, args.dtype) == \
+        (8192, 1024, 4096, 16, 2, "torch", "float16")
