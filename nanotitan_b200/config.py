@@ -121,6 +121,9 @@ class CheckpointConfig(_Strict):
     dir: str = ""
     every_steps: NonNegativeInt = 0    # 0 disables periodic saves
     resume: bool = False
+    # also store the optimizer state per parameter, so that `consolidate --with-optimizer` + `--init-from` can
+    # continue the run on another dp x pp x ep layout (costs a gather of the sharded state at every save)
+    portable_optimizer: bool = False
 
 
 class FaultConfig(_Strict):

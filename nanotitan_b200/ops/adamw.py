@@ -27,6 +27,7 @@ class _Chunk:
         self.bucket = bucket
         self.params, self.spans = params, spans
         self.fused_by_engine = False
+        self.group, self.group_size = None, 1  # the data-parallel group the bucket is reduced over
         n = bucket.buffer.numel()
         self.owned = (0, n)  # the part of the bucket whose optimizer state lives here
         if engine is not None:
@@ -69,6 +70,7 @@ class FusedAdamW(torch.optim.Optimizer):
             for b in red.buckets:
                 engine = red._engine_for(b) if hasattr(red, "_engine_for") else None
                 chunk = _Chunk(b, b.params, b.spans, engine)
+                chunk.group, chunk.group_size = red.process_group, red.group_size
                 if engine is not None:
                     engine.bind_optimizer(b, chunk.flat_param, chunk.master, chunk.exp_avg, chunk.exp_avg_sq, self)
                     chunk.fused_by_engine = True
@@ -173,6 +175,51 @@ class FusedAdamW(torch.optim.Optimizer):
         """Bytes of fp32 optimizer state (master + two moments) held by this rank."""
         self._ensure_layout()
         return sum(3 * 4 * c.master.numel() for c in self._chunks)
+
+    # ------------------------------------------------------------------ layout-independent state
+    def per_parameter_state(self, names: dict[int, str]) -> dict[str, dict[str, torch.Tensor]]:
+        """fp32 master weights and both moments of every parameter, whole, on the host, keyed by
+        `names[id(parameter)]`: the form that does not depend on buckets or on how the state is sharded.
+        Collective over each sharded bucket's data-parallel group (every rank gathers the other ranks' slices)."""
+        import torch.distributed as dist
+
+        self._ensure_layout()
+        out: dict[str, dict[str, torch.Tensor]] = {}
+        for c in self._chunks:
+            n = c.flat_param.numel()
+            whole = {}
+            for key in ("master", "exp_avg", "exp_avg_sq"):
+                mine = getattr(c, key)
+                if tuple(c.owned) == (0, n):
+                    whole[key] = mine.detach().cpu()
+                    continue
+                width = ((n // 8 + c.group_size - 1) // c.group_size) * 8  # the slice width `owned_slice` hands out
+                padded = torch.zeros(width, dtype=torch.float32, device=mine.device)
+                padded[: mine.numel()].copy_(mine)
+                parts = [torch.empty_like(padded) for _ in range(c.group_size)]
+                dist.all_gather(parts, padded, group=c.group)
+                whole[key] = torch.cat(parts)[:n].cpu()
+            for p, (lo, hi) in zip(c.params, c.spans):
+                out[names[id(p)]] = {key: whole[key][lo:hi].view(p.shape).clone() for key in whole}
+        return out
+
+    def load_per_parameter_state(self, state: dict[str, dict[str, torch.Tensor]], names: dict[int, str], step: int) -> None:
+        """Inverse of `per_parameter_state` for whatever layout this run has: every rank keeps what falls into
+        the slices it owns and rewrites the stored parameters there from the master weights."""
+        self._ensure_layout()
+        self._step = step
+        with torch.no_grad():
+            for c in self._chunks:
+                olo, ohi = c.owned
+                for p, (lo, hi) in zip(c.params, c.spans):
+                    rec = state[names[id(p)]]
+                    a, b = max(lo, olo), min(hi, ohi)
+                    if a >= b:
+                        continue
+                    for key in ("master", "exp_avg", "exp_avg_sq"):
+                        src = rec[key].reshape(-1).to(torch.float32)
+                        getattr(c, key)[a - olo : b - olo].copy_(src[a - lo : b - lo])
+                c.flat_param[olo:ohi].copy_(c.master)
 
     def state_dict(self):
         self._ensure_layout()

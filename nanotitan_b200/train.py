@@ -43,6 +43,9 @@ def parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--resume", default="", help="Checkpoint directory to resume from.")
     parser.add_argument("--synthetic-data", action="store_true",
                         help="Uniform-random token ids instead of the token file.")
+    parser.add_argument("--init-from", default="",
+                        help="File written by `python -m nanotitan_b200.utils.checkpoint consolidate [--with-optimizer]`: "
+                             "start from those weights (and optimizer state, step and token count) on this run's layout.")
     parser.add_argument("--eval-batches", type=int, default=20,
                         help="Validation batches per rank and evaluation (trainer.eval_every_step != -1).")
     parser.add_argument("config", help="TOML config path, optionally prefixed with '@'.")
@@ -129,6 +132,28 @@ def main(argv=None) -> None:
             if state.get("data"):
                 epoch, batches_done = state["data"]["epoch"], state["data"]["batches_done"]
             logger.info("resumed from %s at step %d", found, step)
+
+    if args.init_from and step == 0:
+        from nanotitan_b200.utils.checkpoint import load_full_optimizer, load_full_state
+
+        full = torch.load(args.init_from, map_location="cpu", weights_only=False)
+        if "model" in full and isinstance(full["model"], dict):
+            load_full_state(model, full["model"])
+            if full.get("optimizer") is not None:
+                load_full_optimizer(model, optimizer, full["optimizer"])
+            elif hasattr(optimizer, "set_master_weights"):
+                optimizer.set_master_weights({id(p): p.detach() for p in model.parameters()})
+            step, tokens_seen = int(full.get("step", 0)), int(full.get("tokens_seen", 0))
+            if full.get("data") and full.get("data_world_size") == dims.data_world_size:
+                epoch, batches_done = full["data"]["epoch"], full["data"]["batches_done"]
+            elif step:
+                logger.warning("the data is sharded over %d ranks now (%s when saved): the data order starts over",
+                               dims.data_world_size, full.get("data_world_size"))
+        else:  # a bare state dict
+            load_full_state(model, full)
+            if hasattr(optimizer, "set_master_weights"):
+                optimizer.set_master_weights({id(p): p.detach() for p in model.parameters()})
+        logger.info("initialised from %s at step %d", args.init_from, step)
 
     heartbeat = Heartbeat(cfg.fault.heartbeat_dir, dims.global_rank) if cfg.fault.heartbeat_dir else None
     if heartbeat is not None:
@@ -250,7 +275,8 @@ def main(argv=None) -> None:
                     every = cfg.checkpoint.every_steps
                     if cfg.checkpoint.dir and every and step % every == 0:
                         check_peers()
-                        save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg, data_state())
+                        save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg, data_state(),
+                                        cfg.checkpoint.portable_optimizer)
                     if step >= cfg.max_steps:
                         break
                 else:  # the epoch ran out (no break): the next one starts from its first batch
@@ -262,7 +288,8 @@ def main(argv=None) -> None:
                 in_flight = None
         if cfg.checkpoint.dir:
             check_peers()
-            save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg, data_state())
+            save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg, data_state(),
+                                        cfg.checkpoint.portable_optimizer)
     finally:
         if heartbeat is not None:
             heartbeat.leave(step)

@@ -24,14 +24,19 @@ def _rank_file(step_dir: Path, rank: int) -> Path:
     return step_dir / f"rank_{rank:05d}.pt"
 
 
-def save_checkpoint(directory, step: int, tokens_seen: int, model, optimizer, dims, cfg=None, data_state=None) -> Path:
+def save_checkpoint(directory, step: int, tokens_seen: int, model, optimizer, dims, cfg=None, data_state=None,
+                    portable_optimizer: bool = False) -> Path:
     """`data_state` is the loader position ({"epoch", "batches_done"}): a resumed run continues with the batch
-    the interrupted one would have taken next."""
+    the interrupted one would have taken next.  `portable_optimizer` also stores the optimizer state per
+    parameter (whole fp32 tensors under the parameter's name), from which `consolidate_optimizer` +
+    `load_full_optimizer` restore it on any dp x pp x ep layout; the bucket-shaped state that is always stored
+    resumes on the same layout only."""
     step_dir = Path(directory) / f"step_{step:08d}"
     step_dir.mkdir(parents=True, exist_ok=True)
     payload = {
         "model": {k: v.detach().clone().cpu() for k, v in model.state_dict().items()},
         "optimizer": optimizer.state_dict() if optimizer is not None else None,
+        "optimizer_by_name": _optimizer_by_name(model, optimizer, dims) if portable_optimizer else None,
         "step": step,
         "tokens_seen": tokens_seen,
         "data": dict(data_state) if data_state else None,
@@ -62,11 +67,38 @@ def save_checkpoint(directory, step: int, tokens_seen: int, model, optimizer, di
         dist.barrier()
     if dims.global_rank == 0:
         manifest = {"step": step, "tokens_seen": tokens_seen, "world_size": dims.world_size,
+                    "data": dict(data_state) if data_state else None,
+                    "data_world_size": getattr(dims, "data_world_size", None),
                     "config": cfg.model_dump(mode="json") if cfg is not None and hasattr(cfg, "model_dump") else None}
         mtmp = step_dir / "manifest.tmp"
         mtmp.write_text(json.dumps(manifest, indent=2, default=str))
         os.replace(mtmp, step_dir / "manifest.json")
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()  # every rank returns to a complete checkpoint (it may read it back at once)
     return step_dir
+
+
+def _parameter_names(model) -> dict[int, str]:
+    return {id(p): name for name, p in model.named_parameters()}
+
+
+def _optimizer_by_name(model, optimizer, dims):
+    names = _parameter_names(model)
+    if hasattr(optimizer, "per_parameter_state"):  # FusedAdamW: flat buckets, possibly sharded
+        step, state = optimizer._step, optimizer.per_parameter_state(names)  # collective: every rank takes part
+    else:  # torch.optim.AdamW: the parameters are their own master weights
+        step, state = 0, {}
+        for group in optimizer.param_groups:
+            for p in group["params"]:
+                st = optimizer.state.get(p, {})
+                zeros = torch.zeros(p.shape, dtype=torch.float32)
+                state[names[id(p)]] = {"master": p.detach().float().cpu().clone(),
+                                       "exp_avg": st["exp_avg"].detach().float().cpu().clone() if "exp_avg" in st else zeros,
+                                       "exp_avg_sq": st["exp_avg_sq"].detach().float().cpu().clone() if "exp_avg_sq" in st else zeros.clone()}
+                step = max(step, int(st.get("step", 0)))
+    if dims.dp_rank != 0:
+        return None  # replicas of dp rank 0: nothing new to store
+    return {"step": step, "state": state}
 
 
 def is_complete(step_dir) -> bool:
@@ -121,19 +153,22 @@ def load_checkpoint(step_dir, model, optimizer, dims) -> dict:
     return {"step": payload["step"], "tokens_seen": payload["tokens_seen"], "data": payload.get("data")}
 
 
-def consolidate(step_dir) -> dict[str, torch.Tensor]:
-    """Merge the dp_rank-0 shards of every (pp, ep) coordinate into the state dict a
-    single-process model (pp_size = ep_size = 1) would have."""
+def _load_shards(step_dir) -> list[dict]:
     if not is_complete(step_dir):
         raise FileNotFoundError(f"{step_dir} is not a complete checkpoint (manifest or rank shards missing)")
     shards = [torch.load(p, map_location="cpu", weights_only=False) for p in sorted(Path(step_dir).glob("rank_*.pt"))]
-    shards = [s for s in shards if s["coords"]["dp_rank"] == 0]
+    return [s for s in shards if s["coords"]["dp_rank"] == 0]
+
+
+def _merge(shards: list[dict], tensors_of) -> dict[str, torch.Tensor]:
+    """Single-process view of per-shard {stage-local key: tensor} maps (`tensors_of(shard)`): global block
+    indices, expert slices concatenated in expert-rank order, keys in `state_dict()` order."""
     merged: dict[str, torch.Tensor] = {}
     expert_parts: dict[str, dict[int, torch.Tensor]] = {}
     seen: list[str] = []  # keys in the order a model lists them within a block
     for s in shards:
         shift = (s["spec"]["layer_start"] + 1) - (1 if s["spec"]["has_token_embed"] else 0)
-        for key, value in s["model"].items():
+        for key, value in tensors_of(s).items():
             m = re.match(r"blocks\.(\d+)\.(.*)", key)
             local, rest = int(m.group(1)), m.group(2)
             if rest.startswith(("token_embed", "position_embed")):
@@ -151,6 +186,23 @@ def consolidate(step_dir) -> dict[str, torch.Tensor]:
     # blocks in ascending order, keys of a block in the model's own order: the order of `state_dict()`
     ordered = sorted(range(len(seen)), key=lambda i: (int(seen[i].split(".")[1]), i))
     return {seen[i]: merged[seen[i]] for i in ordered if seen[i] in merged}
+
+
+def consolidate(step_dir) -> dict[str, torch.Tensor]:
+    """Merge the dp_rank-0 shards of every (pp, ep) coordinate into the state dict a
+    single-process model (pp_size = ep_size = 1) would have."""
+    return _merge(_load_shards(step_dir), lambda s: s["model"])
+
+
+def consolidate_optimizer(step_dir) -> dict:
+    """{"step": n, "state": {"master" | "exp_avg" | "exp_avg_sq": {single-process parameter name: fp32 tensor}}} of a
+    checkpoint saved with `portable_optimizer=True`."""
+    shards = _load_shards(step_dir)
+    if any(s.get("optimizer_by_name") is None for s in shards):
+        raise ValueError(f"{step_dir} was saved without the per-parameter optimizer state (checkpoint.portable_optimizer)")
+    state = {key: _merge(shards, lambda s, key=key: {name: rec[key] for name, rec in s["optimizer_by_name"]["state"].items()})
+             for key in ("master", "exp_avg", "exp_avg_sq")}
+    return {"step": shards[0]["optimizer_by_name"]["step"], "state": state}
 
 
 def shard_from_full(full_state: dict[str, torch.Tensor], spec) -> dict[str, torch.Tensor]:
@@ -188,6 +240,25 @@ def load_full_state(model, full_state: dict[str, torch.Tensor]) -> None:
             own[key].copy_(value)
 
 
+def load_full_optimizer(model, optimizer, full: dict) -> None:
+    """Give this rank's optimizer its part of a consolidated optimizer state (`consolidate_optimizer`), whatever the
+    layout: this stage's blocks, this rank's expert slice, and of those the bucket slices this rank owns."""
+    own = {key: shard_from_full(full["state"][key], model.spec) for key in ("master", "exp_avg", "exp_avg_sq")}
+    names = _parameter_names(model)
+    by_name = {name: {key: own[key][name] for key in own} for name in names.values()}
+    if hasattr(optimizer, "load_per_parameter_state"):
+        optimizer.load_per_parameter_state(by_name, names, full["step"])
+        return
+    with torch.no_grad():  # torch.optim.AdamW
+        for group in optimizer.param_groups:
+            for p in group["params"]:
+                rec = by_name[names[id(p)]]
+                p.copy_(rec["master"].to(p.dtype))
+                optimizer.state[p] = {"step": torch.tensor(float(full["step"])),
+                                      "exp_avg": rec["exp_avg"].to(device=p.device, dtype=p.dtype).clone(),
+                                      "exp_avg_sq": rec["exp_avg_sq"].to(device=p.device, dtype=p.dtype).clone()}
+
+
 def main(argv=None) -> int:
     """`python -m nanotitan_b200.utils.checkpoint consolidate <checkpoint dir or step dir> <out.pt>`: write the
     single-process state dict (the reference's key layout) of a sharded checkpoint, e.g. to load it into the
@@ -199,12 +270,20 @@ def main(argv=None) -> int:
     cons = sub.add_parser("consolidate", help="merge the rank shards into one state dict")
     cons.add_argument("checkpoint", help="a step_* folder, or the folder holding them (newest complete one is taken)")
     cons.add_argument("out", help="file to write (torch.save of {key: tensor})")
+    cons.add_argument("--with-optimizer", action="store_true",
+                      help="write {'model': ..., 'optimizer': ...} instead (needs checkpoint.portable_optimizer = true)")
     args = ap.parse_args(argv)
     found = latest_checkpoint(args.checkpoint)
     if found is None:
         raise SystemExit(f"no complete checkpoint under {args.checkpoint}")
     state = consolidate(found)
-    torch.save(state, args.out)
+    manifest = json.loads((found / "manifest.json").read_text())
+    if args.with_optimizer:
+        torch.save({"model": state, "optimizer": consolidate_optimizer(found), "step": manifest["step"],
+                    "tokens_seen": manifest["tokens_seen"], "data": manifest.get("data"),
+                    "data_world_size": manifest.get("data_world_size")}, args.out)
+    else:
+        torch.save(state, args.out)
     n = sum(v.numel() for v in state.values())
     print(f"{found}: {len(state)} tensors, {n / 1e6:.2f} M values -> {args.out}")
     return 0
@@ -212,3 +291,4 @@ def main(argv=None) -> int:
 
 if __name__ == "__main__":
     raise SystemExit(main())
+

@@ -154,3 +154,76 @@ def test_load_refuses_a_different_layout():
     state["chunks"][0]["owned"] = (0, 8)
     with pytest.raises(ValueError, match="slice"):
         FusedAdamW([torch.nn.Parameter(torch.randn(40, 8))], lr=1e-3).load_state_dict(state)
+
+
+# ------------------------------------------------------------------ optimizer state across layouts
+def _build_for(cfg, dims, seed):
+    """Like `_build`, with each reducer on its own group size (an expert-parallel layout has one-rank expert groups)."""
+    from nanotitan_b200.models.model import NanoTitanModel
+    from nanotitan_b200.models.utils import get_model_shard_specs
+    from nanotitan_b200.ops.adamw import FusedAdamW
+    from nanotitan_b200.parallel import PipelineParallel
+    from nanotitan_b200.parallel.reducer import ReducerV1
+
+    torch.manual_seed(seed)
+    model = NanoTitanModel.from_specs(cfg.model, get_model_shard_specs(dims, cfg))
+    groups = model.parameter_sync_groups()
+    reducers = {}
+    for name, group, ranks in (("shared", dims.shared_dp_group, dims.shared_dp_group_ranks),
+                               ("expert", dims.expert_dp_group, dims.expert_dp_group_ranks)):
+        size = len(ranks)
+        engine = HostBucketEngine(group, size, ranks.index(dims.global_rank)) if size > 1 else None
+        reducers[name] = ReducerV1(groups[name], size, group, 1, engine=engine)
+    opt = FusedAdamW(list(model.parameters()), lr=cfg.optim.lr, weight_decay=0.1)
+    opt.bind_reducers(reducers)
+    return model, PipelineParallel(cfg, dims, reducers), opt
+
+
+def _relayout_worker(rank, world, tmp):
+    from pathlib import Path
+
+    from nanotitan_b200.parallel_dims import ParallelDims
+    from nanotitan_b200.utils.checkpoint import (consolidate, consolidate_optimizer, load_full_optimizer, load_full_state,
+                                                 save_checkpoint)
+
+    tmp = Path(tmp)
+    cfg_a = tiny_app_cfg(dp=world, batch=2, dtype="bfloat16", moe_backend="torch")
+    dims_a = ParallelDims(cfg_a.runtime)
+    model, step, opt = _build_for(cfg_a, dims_a, seed=3)
+    assert any(c.master.numel() < c.flat_param.numel() for c in opt._chunks), "nothing is sharded: the test would be empty"
+    for s in range(3):
+        step.train_step(model, random_batch(cfg_a, 100 * s + rank), opt)
+    save_checkpoint(tmp / "a", 3, 0, model, opt, dims_a, cfg_a, portable_optimizer=True)
+    weights_a, optim_a = consolidate(tmp / "a" / "step_00000003"), consolidate_optimizer(tmp / "a" / "step_00000003")
+    assert optim_a["step"] == 3 and set(optim_a["state"]) == {"master", "exp_avg", "exp_avg_sq"}
+    assert set(optim_a["state"]["master"]) == {k for k, v in weights_a.items() if v.is_floating_point()} - _buffers(model)
+    assert any(v.abs().max() > 0 for v in optim_a["state"]["exp_avg"].values())
+
+    # the same two processes as an expert-parallel pair, then as two pipeline stages: other shards, other buckets,
+    # other owners of every slice
+    for name, layout in (("ep", dict(ep=world)), ("pp", dict(pp=world, microbatches=2))):
+        cfg_b = tiny_app_cfg(batch=2, dtype="bfloat16", moe_backend="torch", **layout)
+        dims_b = ParallelDims(cfg_b.runtime)
+        model_b, step_b, opt_b = _build_for(cfg_b, dims_b, seed=99)
+        load_full_state(model_b, weights_a)
+        load_full_optimizer(model_b, opt_b, optim_a)
+        save_checkpoint(tmp / name, 3, 0, model_b, opt_b, dims_b, cfg_b, portable_optimizer=True)
+        weights_b, optim_b = consolidate(tmp / name / "step_00000003"), consolidate_optimizer(tmp / name / "step_00000003")
+        assert list(weights_b) == list(weights_a)
+        for key in weights_a:
+            assert torch.equal(weights_a[key], weights_b[key]), (name, key)
+        for part in ("master", "exp_avg", "exp_avg_sq"):
+            for key, value in optim_a["state"][part].items():
+                assert torch.equal(value, optim_b["state"][part][key]), (name, part, key)
+        assert opt_b._step == 3
+        loss = step_b.train_step(model_b, random_batch(cfg_b, 7 + dims_b.data_rank), opt_b)  # and it trains on
+        assert loss is not None
+
+
+def _buffers(model):
+    return {name for name, _ in model.named_buffers()}
+
+
+@pytest.mark.distributed
+def test_optimizer_state_moves_between_layouts_exactly(tmp_path):
+    run_distributed(_relayout_worker, 2, str(tmp_path))

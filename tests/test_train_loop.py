@@ -165,3 +165,64 @@ def _pipeline_eval_worker(rank, world, tmp):
 @pytest.mark.distributed
 def test_validation_runs_through_the_pipeline_stages(tmp_path):
     run_distributed(_pipeline_eval_worker, 2, str(tmp_path))
+
+
+def _file_cfg(tmp, **over):
+    """A config that trains from a packed token file (the same data whatever max_steps is)."""
+    from nanotitan_b200.data.dataset import write_synthetic_token_file
+
+    tokens = Path(tmp) / "train.bin"
+    if not tokens.exists():
+        write_synthetic_token_file(tokens, 61, 8 * 64 + 1, seed=2)
+    cfg = tiny_app_cfg(**over.pop("layout", {})).model_dump(mode="json")
+    cfg["data"] = {"num_workers": 1, "train_tokens_path": str(tokens), "val_tokens_path": str(tokens)}
+    cfg.update(over)
+    return cfg
+
+
+def _train_from_file(tmp, name, cfg, extra=()):
+    from nanotitan_b200 import train
+    from nanotitan_b200.sweep import dump_toml
+
+    path = Path(tmp) / f"{name}.toml"
+    path.write_text(dump_toml(cfg), encoding="utf-8")
+    train.main([str(path), "--log.level", "WARNING", *extra])
+
+
+def _continue_on_two_stages(rank, world, tmp, full_file):
+    import os
+
+    os.chdir(tmp)
+    cfg = _file_cfg(tmp, layout=dict(pp=2, microbatches=1), max_steps=4,
+                    checkpoint={"dir": str(Path(tmp) / "ckpt_pp"), "every_steps": 0, "resume": False})
+    _train_from_file(tmp, f"stage{rank}", cfg, extra=("--init-from", full_file))
+
+
+@pytest.mark.distributed
+def test_a_run_continues_on_another_layout_from_a_consolidated_checkpoint(tmp_path, monkeypatch):
+    """Four steps on one process; against two steps on one process, consolidated with the optimizer state, then two
+    more steps as two pipeline stages started with --init-from: same final weights."""
+    import torch
+
+    from nanotitan_b200.utils import checkpoint
+
+    monkeypatch.chdir(tmp_path)
+
+    def single(name, steps):
+        cfg = _file_cfg(tmp_path, max_steps=steps, checkpoint={"dir": str(tmp_path / name), "every_steps": 0, "resume": False,
+                                                               "portable_optimizer": True})
+        _train_from_file(tmp_path, name, cfg)
+        return checkpoint.consolidate(checkpoint.latest_checkpoint(tmp_path / name))
+
+    straight = single("straight", 4)
+    half = single("half", 2)
+    assert any(not torch.equal(half[k], straight[k]) for k in straight), "two more steps must change the weights"
+    full = tmp_path / "half_full.pt"
+    assert checkpoint.main(["consolidate", str(tmp_path / "half"), str(full), "--with-optimizer"]) == 0
+    run_distributed(_continue_on_two_stages, 2, str(tmp_path), str(full))
+    found = checkpoint.latest_checkpoint(tmp_path / "ckpt_pp")
+    assert found.name == "step_00000004"
+    resumed = checkpoint.consolidate(found)
+    assert list(resumed) == list(straight)
+    for key in straight:
+        torch.testing.assert_close(resumed[key], straight[key], rtol=1e-5, atol=1e-6, msg=lambda m, k=key: f"{k}: {m}")
