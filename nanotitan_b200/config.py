@@ -124,6 +124,8 @@ class CheckpointConfig(_Strict):
     # also store the optimizer state per parameter, so that `consolidate --with-optimizer` + `--init-from` can
     # continue the run on another dp x pp x ep layout (costs a gather of the sharded state at every save)
     portable_optimizer: bool = False
+    # copy the state to host memory, then serialise and write it from a background thread while training goes on
+    async_save: bool = False
 
 
 class FaultConfig(_Strict):

@@ -26,7 +26,7 @@ from nanotitan_b200.parallel import DataParallel, PipelineParallel
 from nanotitan_b200.parallel_dims import get_parallel_dims
 from nanotitan_b200.profiler import build_profiler
 from nanotitan_b200.utils import load_run_config, reduce_scalars, seed_everything, setup_logging
-from nanotitan_b200.utils.checkpoint import latest_checkpoint, load_checkpoint, save_checkpoint
+from nanotitan_b200.utils.checkpoint import AsyncCheckpointer, latest_checkpoint, load_checkpoint, save_checkpoint
 from nanotitan_b200.utils.heartbeat import Heartbeat, assert_peers_alive
 
 logger = logging.getLogger(__name__)
@@ -239,6 +239,13 @@ def main(argv=None) -> None:
     def data_state() -> dict:
         return {"epoch": epoch, "batches_done": batches_done}
 
+    background = AsyncCheckpointer(cfg.fault.pg_timeout_s) if cfg.checkpoint.async_save else None
+
+    def save() -> None:
+        check_peers()
+        write = background.save if background is not None else save_checkpoint
+        write(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg, data_state(), cfg.checkpoint.portable_optimizer)
+
     try:
         # On GPUs the loop runs one step ahead of its own reporting: step i+1 is launched before the metrics
         # of step i are collected, so reading the losses never leaves the device idle.  On CPU a step's
@@ -274,9 +281,7 @@ def main(argv=None) -> None:
                         evaluate(step - 1)
                     every = cfg.checkpoint.every_steps
                     if cfg.checkpoint.dir and every and step % every == 0:
-                        check_peers()
-                        save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg, data_state(),
-                                        cfg.checkpoint.portable_optimizer)
+                        save()
                     if step >= cfg.max_steps:
                         break
                 else:  # the epoch ran out (no break): the next one starts from its first batch
@@ -287,9 +292,10 @@ def main(argv=None) -> None:
                 report(in_flight)
                 in_flight = None
         if cfg.checkpoint.dir:
-            check_peers()
-            save_checkpoint(cfg.checkpoint.dir, step, tokens_seen, model, optimizer, dims, cfg, data_state(),
-                                        cfg.checkpoint.portable_optimizer)
+            save()
+        if background is not None:
+            background.wait()
+            barrier()  # nobody leaves before rank 0 has seen every shard and written the manifest
     finally:
         if heartbeat is not None:
             heartbeat.leave(step)

@@ -10,9 +10,12 @@ so weights can be exchanged with a reference run.
 """
 from __future__ import annotations
 
+import copy
 import json
 import os
 import re
+import threading
+import time
 from pathlib import Path
 
 import torch
@@ -24,18 +27,18 @@ def _rank_file(step_dir: Path, rank: int) -> Path:
     return step_dir / f"rank_{rank:05d}.pt"
 
 
-def save_checkpoint(directory, step: int, tokens_seen: int, model, optimizer, dims, cfg=None, data_state=None,
-                    portable_optimizer: bool = False) -> Path:
-    """`data_state` is the loader position ({"epoch", "batches_done"}): a resumed run continues with the batch
-    the interrupted one would have taken next.  `portable_optimizer` also stores the optimizer state per
-    parameter (whole fp32 tensors under the parameter's name), from which `consolidate_optimizer` +
-    `load_full_optimizer` restore it on any dp x pp x ep layout; the bucket-shaped state that is always stored
-    resumes on the same layout only."""
-    step_dir = Path(directory) / f"step_{step:08d}"
-    step_dir.mkdir(parents=True, exist_ok=True)
-    payload = {
+def _snapshot(step: int, tokens_seen: int, model, optimizer, dims, data_state, portable_optimizer: bool) -> dict:
+    """Everything one rank stores, copied to host memory: nothing in it aliases tensors that training goes on
+    changing.  Collective when `portable_optimizer` is set (the sharded optimizer state is gathered)."""
+    if optimizer is None:
+        optimizer_state = None
+    elif hasattr(optimizer, "per_parameter_state"):
+        optimizer_state = optimizer.state_dict()  # FusedAdamW: already host copies
+    else:
+        optimizer_state = copy.deepcopy(optimizer.state_dict())  # torch.optim: the dict refers to the live moments
+    return {
         "model": {k: v.detach().clone().cpu() for k, v in model.state_dict().items()},
-        "optimizer": optimizer.state_dict() if optimizer is not None else None,
+        "optimizer": optimizer_state,
         "optimizer_by_name": _optimizer_by_name(model, optimizer, dims) if portable_optimizer else None,
         "step": step,
         "tokens_seen": tokens_seen,
@@ -55,27 +58,104 @@ def save_checkpoint(directory, step: int, tokens_seen: int, model, optimizer, di
             "has_token_embed": model.spec.has_token_embed, "has_unembed_head": model.spec.has_unembed_head,
         },
     }
-    target = _rank_file(step_dir, dims.global_rank)
+
+
+def _manifest(step: int, tokens_seen: int, dims, cfg, data_state) -> dict:
+    return {"step": step, "tokens_seen": tokens_seen, "world_size": dims.world_size,
+            "data": dict(data_state) if data_state else None,
+            "data_world_size": getattr(dims, "data_world_size", None),
+            "config": cfg.model_dump(mode="json") if cfg is not None and hasattr(cfg, "model_dump") else None}
+
+
+def _write_shard(step_dir: Path, rank: int, payload: dict) -> None:
+    step_dir.mkdir(parents=True, exist_ok=True)
+    target = _rank_file(step_dir, rank)
     tmp = target.with_suffix(".tmp")
     torch.save(payload, tmp)
     os.replace(tmp, target)
-    # The manifest means "every shard is on disk": rank 0 writes it only after all ranks have
-    # renamed their file into place.
+
+
+def _write_manifest(step_dir: Path, manifest: dict) -> None:
+    mtmp = step_dir / "manifest.tmp"
+    mtmp.write_text(json.dumps(manifest, indent=2, default=str))
+    os.replace(mtmp, step_dir / "manifest.json")
+
+
+def _step_dir(directory, step: int) -> Path:
+    return Path(directory) / f"step_{step:08d}"
+
+
+def save_checkpoint(directory, step: int, tokens_seen: int, model, optimizer, dims, cfg=None, data_state=None,
+                    portable_optimizer: bool = False) -> Path:
+    """`data_state` is the loader position ({"epoch", "batches_done"}): a resumed run continues with the batch
+    the interrupted one would have taken next.  `portable_optimizer` also stores the optimizer state per
+    parameter (whole fp32 tensors under the parameter's name), from which `consolidate_optimizer` +
+    `load_full_optimizer` restore it on any dp x pp x ep layout; the bucket-shaped state that is always stored
+    resumes on the same layout only."""
     import torch.distributed as dist
 
-    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+    step_dir = _step_dir(directory, step)
+    _write_shard(step_dir, dims.global_rank, _snapshot(step, tokens_seen, model, optimizer, dims, data_state, portable_optimizer))
+    # The manifest means "every shard is on disk": rank 0 writes it only after all ranks have
+    # renamed their file into place.
+    many = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+    if many:
         dist.barrier()
     if dims.global_rank == 0:
-        manifest = {"step": step, "tokens_seen": tokens_seen, "world_size": dims.world_size,
-                    "data": dict(data_state) if data_state else None,
-                    "data_world_size": getattr(dims, "data_world_size", None),
-                    "config": cfg.model_dump(mode="json") if cfg is not None and hasattr(cfg, "model_dump") else None}
-        mtmp = step_dir / "manifest.tmp"
-        mtmp.write_text(json.dumps(manifest, indent=2, default=str))
-        os.replace(mtmp, step_dir / "manifest.json")
-    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        _write_manifest(step_dir, _manifest(step, tokens_seen, dims, cfg, data_state))
+    if many:
         dist.barrier()  # every rank returns to a complete checkpoint (it may read it back at once)
     return step_dir
+
+
+class AsyncCheckpointer:
+    """`save()` copies this rank's state to host memory and returns; a background thread serialises it and
+    renames it into place, so training waits for the copy, not for the disk.  The thread uses no collectives:
+    rank 0's thread writes the manifest once it sees every rank's shard file (it polls the folder, for at most
+    `timeout_s`).  One save is in flight at a time - the next `save()` and `wait()` join the previous one and
+    re-raise what it failed with.  Call `wait()` before the process ends."""
+
+    def __init__(self, timeout_s: float = 600.0):
+        self.timeout_s = timeout_s
+        self._thread: threading.Thread | None = None
+        self._error: BaseException | None = None
+
+    def save(self, directory, step: int, tokens_seen: int, model, optimizer, dims, cfg=None, data_state=None,
+             portable_optimizer: bool = False) -> Path:
+        self.wait()
+        step_dir = _step_dir(directory, step)
+        payload = _snapshot(step, tokens_seen, model, optimizer, dims, data_state, portable_optimizer)
+        manifest = _manifest(step, tokens_seen, dims, cfg, data_state) if dims.global_rank == 0 else None
+        self._thread = threading.Thread(target=self._write, name=f"checkpoint-step-{step}", daemon=True,
+                                        args=(step_dir, dims.global_rank, dims.world_size, payload, manifest))
+        self._thread.start()
+        return step_dir
+
+    def _write(self, step_dir: Path, rank: int, world: int, payload: dict, manifest: dict | None) -> None:
+        try:
+            _write_shard(step_dir, rank, payload)
+            if manifest is None:
+                return
+            deadline = time.monotonic() + self.timeout_s
+            while not all(_rank_file(step_dir, r).exists() for r in range(world)):
+                if time.monotonic() > deadline:
+                    raise TimeoutError(f"{step_dir}: not every rank's shard appeared within {self.timeout_s:.0f} s; "
+                                       "no manifest written, the checkpoint stays incomplete")
+                time.sleep(0.05)
+            _write_manifest(step_dir, manifest)
+        except BaseException as exc:  # noqa: BLE001 - handed to the training thread by wait()
+            self._error = exc
+
+    def in_flight(self) -> bool:
+        return self._thread is not None and self._thread.is_alive()
+
+    def wait(self) -> None:
+        if self._thread is not None:
+            self._thread.join()
+            self._thread = None
+        if self._error is not None:
+            error, self._error = self._error, None
+            raise RuntimeError(f"asynchronous checkpoint failed: {error}") from error
 
 
 def _parameter_names(model) -> dict[int, str]:
