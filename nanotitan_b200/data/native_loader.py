@@ -81,13 +81,16 @@ def skip_batches(loader, n: int):
 
 
 def make_train_loader(dataset, sampler, batch_size: int, device: torch.device, num_workers: int):
-    """The native loader for packed token files when the extension is built, else a torch DataLoader."""
+    """The native loader for packed token files when the extension is built (and `NT_NATIVE_LOADER` is not 0),
+    else a torch DataLoader."""
+    import os
+
     from torch.utils.data import DataLoader
 
     from nanotitan_b200.data.dataset import PackedTokenDataset
     from nanotitan_b200.ops.ext import have_ext
 
-    if isinstance(dataset, PackedTokenDataset) and have_ext():
+    if isinstance(dataset, PackedTokenDataset) and have_ext() and os.environ.get("NT_NATIVE_LOADER", "1") != "0":
         return NativeTokenLoader(dataset.path, dataset.seq_len, batch_size, sampler, device, threads=max(1, min(num_workers, 4)))
     return DataLoader(dataset, batch_size=batch_size, shuffle=False, sampler=sampler, num_workers=num_workers,
                       pin_memory=device.type == "cuda", drop_last=True)
