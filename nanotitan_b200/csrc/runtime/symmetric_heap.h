@@ -290,6 +290,7 @@ class SymmetricHeap {
     if (mc_here) {
       if (rank_ == 0) {
         a.mc = api_.multicast_create(world_, a.size);
+        undo.add([&] { api_.release(a.mc); });
         int fd = api_.export_fd(a.mc);
         FdGuard guard(fd);
         for (int p = 1; p < world_; ++p) channel_.send(p, kMulticast, a.id, 0, fd);
@@ -298,8 +299,8 @@ class SymmetricHeap {
         FdGuard guard(got.fd);
         if (got.fd < 0) throw std::runtime_error("symmetric heap: rank 0 sent no multicast handle");
         a.mc = api_.import_fd(got.fd);
+        undo.add([&] { api_.release(a.mc); });
       }
-      undo.add([&] { api_.release(a.mc); });
       api_.multicast_add_device(a.mc, device_);
       barrier();  // the driver wants every device added before the first bind
       api_.multicast_bind(a.mc, a.local, a.size);
