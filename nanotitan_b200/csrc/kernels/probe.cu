@@ -1,5 +1,5 @@
 // Self-test of the soft-failure path: a kernel waits on an mbarrier that nothing will ever
-// complete, with a short cycle budget; the wait gives up, records a status word and the kernel
+// complete, with a short cycle limit; the wait gives up, records a status word and the kernel
 // returns normally, so the context stays usable.  This is how the bounded waits of the tcgen05
 // and NVLink kernels are exercised without faulting, trapping or hanging the GPU.
 #include <ATen/cuda/CUDAContext.h>
