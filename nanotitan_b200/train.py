@@ -250,7 +250,7 @@ def main(argv=None) -> None:
         # On GPUs the loop runs one step ahead of its own reporting: step i+1 is launched before the metrics
         # of step i are collected, so reading the losses never leaves the device idle.  On CPU a step's
         # collectives block the host, there is nothing to overlap, and every step is reported at once.
-        run_ahead = device.type == "cuda"
+        run_ahead = os.environ.get("NT_RUN_AHEAD", "1" if device.type == "cuda" else "0") == "1"
         in_flight = None
         with profiler as prof:
             while step < cfg.max_steps:

@@ -226,3 +226,24 @@ def test_a_run_continues_on_another_layout_from_a_consolidated_checkpoint(tmp_pa
     assert list(resumed) == list(straight)
     for key in straight:
         torch.testing.assert_close(resumed[key], straight[key], rtol=1e-5, atol=1e-6, msg=lambda m, k=key: f"{k}: {m}")
+
+
+def test_reporting_one_step_behind_still_reports_every_step_once(tmp_path, monkeypatch):
+    """On GPUs the loop launches step i+1 before it collects the metrics of step i; forced on here, the same
+    bookkeeping must log every step exactly once and in order, the last one after the loop, with the token
+    counts of the step it belongs to."""
+    monkeypatch.chdir(tmp_path)
+    monkeypatch.setenv("NT_RUN_AHEAD", "1")
+    path = _write_cfg(tmp_path, "ahead.toml", max_steps=5,
+                      checkpoint={"dir": str(tmp_path / "ckpt"), "every_steps": 2, "resume": False})
+    logged = []
+    _run_main(path, logged)
+    train_steps = [(s, m) for s, m in logged if "train/ce_loss" in m]
+    assert [s for s, _ in train_steps] == [0, 1, 2, 3, 4]
+    per_step = train_steps[0][1]["train/tokens_per_step"]
+    assert [m["train/total_tokens_seen"] for _, m in train_steps] == [per_step * (i + 1) for i in range(5)]
+
+    monkeypatch.setenv("NT_RUN_AHEAD", "0")
+    again = []
+    _run_main(_write_cfg(tmp_path, "now.toml", max_steps=5), again)
+    assert [m["train/ce_loss"] for _, m in again] == [m["train/ce_loss"] for _, m in train_steps], "same run, same losses"
