@@ -21,7 +21,7 @@ import torch
 
 class NativeTokenLoader:
     def __init__(self, path: str, seq_len: int, batch_size: int, sampler, device: torch.device, depth: int = 4,
-                 threads: int = 2, timeout_s: float = 120.0, ext=None):
+                 threads: int = 2, timeout_s: float = 120.0, ext=None, views: bool | None = None):
         if ext is None:
             from nanotitan_b200.ops.ext import get_ext
 
@@ -29,6 +29,7 @@ class NativeTokenLoader:
         assert depth >= 3, "two batches stay with the consumer while the next one is filled"
         self.sampler, self.batch_size, self.seq_len, self.depth = sampler, batch_size, seq_len, depth
         self.on_gpu = device.type == "cuda"
+        self.views = self.on_gpu if views is None else views  # hand out ring slots themselves, not copies
         self.timeout_ms = int(timeout_s * 1000)
         self._loader = ext.TokenWindowLoader(str(path), seq_len, batch_size, depth, threads)
         self.num_sequences = int(self._loader.num_sequences)
@@ -52,7 +53,7 @@ class NativeTokenLoader:
                     event = torch.cuda.Event()
                     event.record()
                     held[-1] = (held[-1][0], event)
-                while len(held) > (1 if self.on_gpu else 0):
+                while len(held) > (1 if self.views else 0):
                     slot, event = held.popleft()
                     if event is not None:
                         event.synchronize()
@@ -62,7 +63,7 @@ class NativeTokenLoader:
                     return
                 held.append((slot, None))
                 x, y = self._slots[slot, 0], self._slots[slot, 1]
-                yield (x, y) if self.on_gpu else (x.clone(), y.clone())
+                yield (x, y) if self.views else (x.clone(), y.clone())
         finally:
             self._loader.stop()
 

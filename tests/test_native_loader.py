@@ -87,3 +87,25 @@ def test_a_resumed_epoch_starts_where_the_interrupted_one_stopped(tmp_path):
             assert torch.equal(ax, bx) and torch.equal(ay, by)
         assert len(list(loader)) == 7  # the skip applies to one epoch only
         assert list(skip_batches(loader, 7)) == [] and list(skip_batches(loader, 9)) == []
+
+
+@needs_ext
+def test_ring_slots_handed_out_as_views_stay_valid_for_two_requests(tmp_path):
+    """The GPU form of the loader yields the pinned ring slots themselves; a batch must stay intact while the next
+    one is requested (its host-to-device copy may still be reading it) and its slot may be refilled only after that."""
+    from nanotitan_b200.data.native_loader import NativeTokenLoader
+
+    path = write_synthetic_token_file(tmp_path / "tokens.bin", 1000, 8 * 24 + 1, seed=6)
+    dataset = PackedTokenDataset(path, 8)
+    loader = NativeTokenLoader(path, 8, 2, list(range(len(dataset))), torch.device("cpu"), depth=3, threads=2, views=True)
+    want = [torch.stack([dataset[2 * b][0], dataset[2 * b + 1][0]]) for b in range(12)]
+    previous = None
+    seen = 0
+    for b, (x, _) in enumerate(loader):
+        assert x.data_ptr() == loader._slots[b % 3, 0].data_ptr(), "a view of the ring, not a copy"
+        assert torch.equal(x, want[b])
+        if previous is not None:
+            assert torch.equal(previous, want[b - 1]), "the batch before this one was overwritten too early"
+        previous = x
+        seen += 1
+    assert seen == 12
