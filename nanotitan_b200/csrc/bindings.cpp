@@ -48,6 +48,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("wd"), py::arg("grad_scale"), py::arg("want_sq"),
         py::arg("bc_dev") = py::none());
   m.def("router_topk", &nt::router_topk);
+  m.def("router_from_logits", &nt::router_from_logits, "router_topk's outputs from fp32 logits [T, E]");
   m.def("router_bwd", &nt::router_bwd);
   m.def("assign_slots", &nt::assign_slots);
   m.def("pack_fwd", &nt::pack_fwd);

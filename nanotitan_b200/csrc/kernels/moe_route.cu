@@ -154,6 +154,98 @@ router_topk_kernel(const T* __restrict__ x, const WT* __restrict__ w, float* __r
   }
 }
 
+// The routing half of router_topk_kernel for logits that were computed elsewhere (a tensor-core GEMM): softmax,
+// top-k with the same tie rule, renormalised gates, per-expert counts and the per-block sums of the
+// probabilities.  One warp per token; lane (e % 32) holds expert e in slot e / 32.
+__global__ void __launch_bounds__(RT_WARPS * 32)
+router_from_logits_kernel(const float* __restrict__ logits, float* __restrict__ gates, int* __restrict__ idx,
+                          float* __restrict__ probs, int* __restrict__ counts, float* __restrict__ prob_parts,
+                          long long tokens, int E, int k, StatusWord* __restrict__ status) {
+  __shared__ int s_counts[RT_MAX_E];
+  __shared__ float s_psum[RT_WARPS][RT_MAX_E];
+  float psum[RT_SLOTS];
+#pragma unroll
+  for (int s = 0; s < RT_SLOTS; ++s) psum[s] = 0.f;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) s_counts[e] = 0;
+  __syncthreads();
+  for (long long tok = static_cast<long long>(blockIdx.x) * RT_WARPS + warp; tok < tokens;
+       tok += static_cast<long long>(gridDim.x) * RT_WARPS) {
+    float p[RT_SLOTS];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < RT_SLOTS; ++s) {
+      const int e = s * 32 + lane;
+      p[s] = e < E ? logits[tok * E + e] : -INFINITY;
+      mx = fmaxf(mx, p[s]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int s = 0; s < RT_SLOTS; ++s) {
+      p[s] = (s * 32 + lane < E) ? __expf(p[s] - mx) : 0.f;
+      sum += p[s];
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int s = 0; s < RT_SLOTS; ++s) {
+      p[s] *= inv;
+      psum[s] += p[s];
+      const int e = s * 32 + lane;
+      if (e < E) probs[tok * E + e] = p[s];
+    }
+    float taken_sum = 0.f;
+    float my_gate = 0.f;
+    int my_e = 0;
+    for (int j = 0; j < k; ++j) {
+      float best = -1.f;
+      int best_e = 0x7fffffff;
+#pragma unroll
+      for (int s = 0; s < RT_SLOTS; ++s) {
+        const int e = s * 32 + lane;
+        if (e < E && p[s] > best) { best = p[s]; best_e = e; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+        if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+      }
+      if (best_e >= E) {  // a row of NaN: fixed experts, neutral weight, and a record of it (see router_topk_kernel)
+        best_e = j;
+        best = 0.f;
+        if (lane == 0) report_status(status, kStatusBadArgument, kKernelPack, static_cast<uint32_t>(tok));
+      }
+#pragma unroll
+      for (int s = 0; s < RT_SLOTS; ++s)
+        if (s * 32 + lane == best_e) p[s] = -2.f;
+      taken_sum += best;
+      if (lane == j) { my_gate = best; my_e = best_e; }
+    }
+    if (!(taken_sum > 0.f)) {
+      my_gate = 1.f;
+      taken_sum = static_cast<float>(k);
+    }
+    if (lane < k) {
+      gates[tok * k + lane] = my_gate / taken_sum;
+      idx[tok * k + lane] = my_e;
+      atomicAdd(&s_counts[my_e], 1);
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < RT_SLOTS; ++s)
+    if (s * 32 + lane < E) s_psum[warp][s * 32 + lane] = psum[s];
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    if (s_counts[e] != 0) atomicAdd(&counts[e], s_counts[e]);
+    float t = 0.f;
+#pragma unroll
+    for (int w2 = 0; w2 < RT_WARPS; ++w2) t += s_psum[w2][e];
+    prob_parts[static_cast<long long>(blockIdx.x) * E + e] = t;
+  }
+}
+
 // out[c] = scale * sum over `parts` rows of in[p][c]; 8 row groups per column, added in a fixed order.
 __global__ void scaled_column_sum_kernel(const float* __restrict__ in, float* __restrict__ out, int parts, int cols, float scale) {
   __shared__ float red[8][33];
@@ -330,6 +422,39 @@ std::vector<at::Tensor> router_topk(const at::Tensor& x, const at::Tensor& w, in
             probs.data_ptr<float>(), counts.data_ptr<int>(), parts.data_ptr<float>(), tokens, d, E, static_cast<int>(k), device_status_word());
       });
     });
+    NT_KERNEL_CHECK();
+    scaled_column_sum_kernel<<<(E + 31) / 32, dim3(32, 8), 0, stream>>>(parts.data_ptr<float>(), probs_mean.data_ptr<float>(), grid, E,
+                                                                         1.f / static_cast<float>(tokens));
+    NT_KERNEL_CHECK();
+  }
+  return {gates, idx, probs, counts, probs_mean};
+}
+
+// The same five outputs as router_topk from fp32 logits [T, E] (e.g. of the tensor-core GEMM, which is the faster
+// way to form them once experts x width no longer fits the caches router_topk_kernel reads the router matrix through).
+std::vector<at::Tensor> router_from_logits(const at::Tensor& logits, int64_t k) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.is_contiguous() && logits.scalar_type() == at::kFloat,
+              "router_from_logits: logits fp32 [T, E], contiguous");
+  c10::cuda::CUDAGuard guard(logits.device());
+  const long long tokens = logits.size(0);
+  const int E = static_cast<int>(logits.size(1));
+  TORCH_CHECK(E >= 1 && E <= RT_MAX_E, "router_from_logits supports up to ", RT_MAX_E, " experts");
+  TORCH_CHECK(k >= 1 && k <= E && k <= 32, "router_from_logits: 1 <= k <= min(E, 32)");
+  auto f32 = logits.options();
+  auto i32 = logits.options().dtype(at::kInt);
+  auto gates = at::empty({tokens, k}, f32);
+  auto idx = at::empty({tokens, k}, i32);
+  auto probs = at::empty({tokens, E}, f32);
+  auto counts = at::zeros({E}, i32);
+  auto probs_mean = tokens > 0 ? at::empty({E}, f32) : at::zeros({E}, f32);
+  if (tokens > 0) {
+    const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+    const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>((tokens + RT_WARPS - 1) / RT_WARPS, 8LL * sms)));
+    auto parts = at::empty({grid, E}, f32);
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+    router_from_logits_kernel<<<grid, RT_WARPS * 32, 0, stream>>>(logits.data_ptr<float>(), gates.data_ptr<float>(), idx.data_ptr<int>(),
+                                                                  probs.data_ptr<float>(), counts.data_ptr<int>(), parts.data_ptr<float>(),
+                                                                  tokens, E, static_cast<int>(k), device_status_word());
     NT_KERNEL_CHECK();
     scaled_column_sum_kernel<<<(E + 31) / 32, dim3(32, 8), 0, stream>>>(parts.data_ptr<float>(), probs_mean.data_ptr<float>(), grid, E,
                                                                          1.f / static_cast<float>(tokens));

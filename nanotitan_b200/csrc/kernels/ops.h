@@ -99,6 +99,7 @@ void ep_push_rows(const at::Tensor& src, const at::Tensor& dst_peers, int64_t ds
 
 // ---- MoE routing / dispatch
 std::vector<at::Tensor> router_topk(const at::Tensor& x, const at::Tensor& w, int64_t k);
+std::vector<at::Tensor> router_from_logits(const at::Tensor& logits, int64_t k);  // same outputs, logits formed elsewhere
 std::vector<at::Tensor> router_bwd(const at::Tensor& gates, const at::Tensor& idx, const at::Tensor& probs,
                                    const c10::optional<at::Tensor>& dgates, const c10::optional<at::Tensor>& dprobs,
                                    const c10::optional<at::Tensor>& dprobs_mean, const at::Tensor& like);

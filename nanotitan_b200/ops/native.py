@@ -327,6 +327,32 @@ def linear_cross_entropy(x, w_unembed, targets):
 
 
 # ------------------------------------------------------------------------------- MoE routing
+def split_bf16(w: torch.Tensor, dtype: torch.dtype) -> tuple[torch.Tensor, torch.Tensor]:
+    """w = head + remainder with both parts in a 16-bit `dtype`: the head is w rounded, the remainder what the
+    rounding lost, rounded again.  Two 16-bit products then give x . w to about 2^-16 of |x||w| instead of the
+    2^-8 (bf16) or 2^-11 (fp16) of one."""
+    head = w.to(dtype)
+    return head, (w.float() - head.float()).to(dtype)
+
+
+def router_logits_tc(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """fp32 router logits x . w^T [T, E] on the tcgen05 GEMM from 16-bit tokens and the fp32 router matrix: two
+    thin products (head and remainder of w) accumulated in fp32."""
+    head, rest = split_bf16(w, x.dtype)
+    logits = torch.empty(x.shape[0], w.shape[0], dtype=torch.float32, device=x.device)
+    gemm_tc(x, False, [head], False, [logits])
+    gemm_tc(x, False, [rest], False, [logits], accumulate=True)
+    return logits
+
+
+def _router_on_tensor_cores(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """`NT_ROUTER_GEMM=1`: form the router logits with the GEMM kernel instead of inside `router_topk`, which
+    reads the router matrix once per group of four tokens - fine for 8 experts x 512, slow for 64 x 2048."""
+    if os.environ.get("NT_ROUTER_GEMM", "0") != "1":
+        return False
+    return x.dim() == 2 and tc_ok(x) and w.dim() == 2 and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0 and x.shape[0] > 0
+
+
 class _Router(torch.autograd.Function):
     """Fused fp32 router.  Outputs: gates [T,k] (grad -> x and w), ids [T,k], probs [T,E] and their
     column means [E], counts [E].  The gradient of the probabilities (the load-balancing loss) reaches
@@ -336,7 +362,10 @@ class _Router(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w, k, aux_to_tokens=False):
-        gates, idx, probs, counts, probs_mean = get_ext().router_topk(x.contiguous(), w.contiguous(), k)
+        if _router_on_tensor_cores(x, w):
+            gates, idx, probs, counts, probs_mean = get_ext().router_from_logits(router_logits_tc(x, w), k)
+        else:
+            gates, idx, probs, counts, probs_mean = get_ext().router_topk(x.contiguous(), w.contiguous(), k)
         ctx.save_for_backward(x, w, gates, idx, probs)
         ctx.aux_to_tokens = aux_to_tokens
         ctx.mark_non_differentiable(idx, counts)

@@ -152,6 +152,32 @@ def test_router_topk_matches_torch(tokens, d, E, k):
     torch.testing.assert_close(probs_mean, p_ref.mean(dim=0), rtol=1e-4, atol=1e-6)
 
 
+@pytest.mark.parametrize("tokens,d,E,k", [(1000, 128, 8, 2), (4096, 512, 64, 8), (37, 64, 64, 8)])
+def test_router_from_gemm_logits_matches_the_fused_router(tokens, d, E, k, monkeypatch):
+    """The other way to the same five outputs: logits from two thin tcgen05 products, routing kernel on the logits.
+    Runs only when asked for (NT_TEST_ROUTER_GEMM=1): `router_from_logits_kernel` has not run on a GPU yet."""
+    import os
+
+    if os.environ.get("NT_TEST_ROUTER_GEMM") != "1":
+        pytest.skip("set NT_TEST_ROUTER_GEMM=1 to run the tensor-core router path")
+    from nanotitan_b200.ops import native
+
+    torch.manual_seed(4)
+    x = torch.randn(tokens, d, device="cuda").bfloat16()
+    w = torch.randn(E, d, device="cuda") * 0.3
+    fused = _ext().router_topk(x, w, k)
+    monkeypatch.setenv("NT_ROUTER_GEMM", "1")
+    assert native._router_on_tensor_cores(x, w)
+    split = _ext().router_from_logits(native.router_logits_tc(x, w), k)
+    torch.cuda.synchronize()
+    assert _ext().read_status(True)[0] == 0
+    for a, b, name in zip(fused, split, ("gates", "idx", "probs", "counts", "probs_mean")):
+        if name in ("idx", "counts"):
+            assert (a != b).float().mean() < 2e-3, name  # a near-tie may fall the other way
+        else:
+            torch.testing.assert_close(a, b, rtol=2e-3, atol=2e-5, msg=lambda m, n=name: f"{n}: {m}")
+
+
 def test_slots_are_expert_major_in_token_order():
     torch.manual_seed(5)
     tokens, E, k = 5000, 8, 2

@@ -57,3 +57,38 @@ def test_unembed_loss_panels_match_the_unfused_form(monkeypatch, rows, chunk, wa
     torch.testing.assert_close(loss, want, rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(x.grad, x2.grad, rtol=1e-4, atol=1e-6)
     torch.testing.assert_close(w.grad, w2.grad, rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype,bound", [(torch.bfloat16, 2e-4), (torch.float16, 2e-5)])
+def test_two_16_bit_products_recover_the_fp32_router_logits(monkeypatch, dtype, bound):
+    """The router matrix is fp32; the tensor cores take 16-bit operands.  Head + remainder keeps the logits within
+    ~2^-16 of the fp32 product (one rounded product is 100x worse), so top-k picks and probabilities follow the
+    fp32 router."""
+    from nanotitan_b200.ops import native
+
+    monkeypatch.setattr(native, "gemm_tc", _gemm_stand_in)
+    torch.manual_seed(1)
+    tokens, experts, d = 512, 64, 256
+    x = torch.randn(tokens, d).to(dtype)
+    w = torch.randn(experts, d) / d**0.5
+    head, rest = native.split_bf16(w, dtype)
+    assert head.dtype == rest.dtype == dtype
+    want = x.double() @ w.double().t()
+    got = native.router_logits_tc(x, w).double()
+    one = (x.float() @ head.float().t()).double()
+    scale = want.abs().max()
+    assert (got - want).abs().max() / scale < bound
+    assert (one - want).abs().max() > 30 * (got - want).abs().max()
+    assert torch.equal(got.topk(8, dim=1).indices, want.topk(8, dim=1).indices) or \
+        (got.topk(8, dim=1).indices != want.topk(8, dim=1).indices).float().mean() < 1e-3
+
+
+def test_router_path_switch(monkeypatch):
+    from nanotitan_b200.ops import native
+
+    x = torch.zeros(16, 64)
+    w = torch.zeros(8, 64)
+    monkeypatch.delenv("NT_ROUTER_GEMM", raising=False)
+    assert not native._router_on_tensor_cores(x, w)
+    monkeypatch.setenv("NT_ROUTER_GEMM", "1")
+    assert not native._router_on_tensor_cores(x, w)  # not 16-bit tensors on a GPU: stays on the fused kernel
