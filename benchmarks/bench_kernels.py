@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 from pathlib import Path
 
@@ -133,6 +134,9 @@ def bench_moe(iters):
         w = torch.randn(E, d, device="cuda") * 0.1
         ms = timed(lambda: ext.router_topk(x, w, k), iters)
         report(f"router_topk T{T} d{d} E{E} k{k}", ms, nbytes=T * d * 2 + T * E * 4)
+        if os.environ.get("NT_ROUTER_GEMM") == "1":  # the other router path, only when asked for
+            ms = timed(lambda: ext.router_from_logits(native.router_logits_tc(x, w), k), iters)
+            report(f"router via GEMM logits T{T} d{d} E{E} k{k}", ms, nbytes=T * d * 2 * 2 + T * E * 4 * 3)
         gates, idx, probs, counts = ext.router_topk(x, w, k)[:4]
         ms = timed(lambda: ext.assign_slots(idx, counts), iters)
         report(f"assign_slots T{T} E{E} k{k}", ms, nbytes=T * k * 8)
