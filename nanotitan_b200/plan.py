@@ -1,6 +1,6 @@
 """What a configuration puts on each GPU, before any GPU is involved.
 
-    python -m nanotitan_b200.plan configs/moe_3d.toml [--hbm-gb 180] [--json]
+    python -m nanotitan_b200.plan configs/moe_3d.toml [--hbm-gb 180] [--capacity-factor f] [--sustained-tflops t] [--json]
 
 For every distinct (pipeline stage, expert rank) of the layout the model shard is built on the meta device
 (no memory) and the planner reports, per GPU:
@@ -13,7 +13,8 @@ For every distinct (pipeline stage, expert rank) of the layout the model shard i
            nodes save per layer, times the micro-batches a GPipe stage holds in flight.
 
 and compares the sum with the HBM size (180 GB on a B200).  The estimate is labelled as such in the output: it
-counts the saved tensors, not allocator slack or temporaries.  The reference has no counterpart.
+counts the saved tensors, not allocator slack or temporaries.  The last line is the step-time floor: the model
+FLOPs of a step at the sustained GEMM rate of MEASURED_PEAKS.json.  The reference has no counterpart.
 """
 from __future__ import annotations
 
@@ -147,6 +148,37 @@ def plan(cfg: AppConfig, capacity_factor: float = 0.0) -> list[ShardPlan]:
     return list(seen.values())
 
 
+def step_floor(cfg: AppConfig, sustained_tflops: float) -> dict:
+    """Model FLOPs of one optimizer step over the whole job (the trainer's MFU numerator: 6 x active matmul
+    parameters + causal attention, per token) and the time they take at `sustained_tflops` per GPU: the floor any
+    measured step time is compared with."""
+    from nanotitan_b200.train import model_flops_per_token
+
+    rt, m = cfg.runtime, cfg.model
+    with torch.device("meta"):
+        layout = _layout(cfg, 0)
+        layout_full = RankLayout(1, 0, 1, 1, 1, num_experts=m.num_experts)
+        layout_full.ep_group = None
+        whole = NanoTitanModel.from_specs(m, get_model_shard_specs(layout_full, cfg))
+    active = float(whole.active_parameter_count())
+    tokens = cfg.trainer.per_device_batch_size * layout.data_world_size * m.max_seq_len
+    flops = model_flops_per_token(cfg, active) * tokens
+    gpus = rt.dp_size * rt.pp_size * rt.ep_size
+    return {"tokens_per_step": tokens, "tflop_per_step": flops / 1e12, "gpus": gpus,
+            "floor_ms": flops / (sustained_tflops * 1e12 * gpus) * 1e3 if sustained_tflops > 0 else None}
+
+
+def measured_sustained_tflops(default: float = 1400.0) -> float:
+    """`bf16_tflops_sustained` of MEASURED_PEAKS.json next to the package's parent folder, else `default`."""
+    from pathlib import Path
+
+    path = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(path.read_text())["bf16_tflops_sustained"])
+    except (OSError, KeyError, ValueError):
+        return default
+
+
 def render(shards: list[ShardPlan], hbm_gb: float) -> str:
     lines = []
     for s in shards:
@@ -168,13 +200,18 @@ def main(argv=None) -> int:
     ap.add_argument("--hbm-gb", type=float, default=180.0)
     ap.add_argument("--capacity-factor", type=float, default=0.0, help="NT_EP_CAPACITY_FACTOR the run will use (0: worst case)")
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--sustained-tflops", type=float, default=0.0,
+                    help="dense bf16 GEMM rate per GPU for the step-time floor (default: MEASURED_PEAKS.json, else 1400)")
     args = ap.parse_args(argv)
     cfg = load_config(args.config.removeprefix("@"))
     shards = plan(cfg, args.capacity_factor)
+    floor = step_floor(cfg, args.sustained_tflops or measured_sustained_tflops())
     if args.json:
-        print(json.dumps([dict(asdict(s), total=s.total) for s in shards], indent=1))
+        print(json.dumps({"shards": [dict(asdict(s), total=s.total) for s in shards], "step": floor}, indent=1))
     else:
         print(render(shards, args.hbm_gb))
+        print(f"one step: {floor['tokens_per_step']} tokens, {floor['tflop_per_step']:.2f} TFLOP of model math over {floor['gpus']} GPU(s): "
+              f">= {floor['floor_ms']:.2f} ms at {args.sustained_tflops or measured_sustained_tflops():.0f} TFLOP/s per GPU")
     return 0 if all(s.total < args.hbm_gb * GB for s in shards) else 1
 
 

@@ -73,5 +73,7 @@ def test_command_line(tmp_path, capsys):
     assert plan.main([str(path), "--hbm-gb", "0.000001"]) == 1
     assert "DOES NOT FIT" in capsys.readouterr().out
     assert plan.main(["@" + str(path), "--json"]) == 0
-    rows = json.loads(capsys.readouterr().out)
+    out = json.loads(capsys.readouterr().out)
+    rows = out["shards"]
     assert len(rows) == 2 and rows[0]["total"] == sum(rows[0]["bytes"].values())
+    assert out["step"]["gpus"] == 2 and out["step"]["tokens_per_step"] == 2 * 2 * 8 and out["step"]["floor_ms"] > 0
