@@ -168,6 +168,28 @@ def step_floor(cfg: AppConfig, sustained_tflops: float) -> dict:
             "floor_ms": flops / (sustained_tflops * 1e12 * gpus) * 1e3 if sustained_tflops > 0 else None}
 
 
+def nvlink_bytes_per_step(cfg: AppConfig, shard: ShardPlan) -> dict[str, int]:
+    """Bytes one GPU of `shard` sends (and, symmetrically, receives) over NVLink in one step, by cause:
+    gradient buckets (the fused all-reduce moves one bucket out and one in per replica group larger than one),
+    expert exchange (four transfers per MoE layer and micro-batch, the share of rows that leaves the GPU),
+    pipeline boundaries (activations forward, their gradients backward)."""
+    rt, m = cfg.runtime, cfg.model
+    elem = resolve_dtype(m.dtype).itemsize
+    layout = _layout(cfg, shard.ranks[0])
+    out: dict[str, int] = {}
+    replicas = {"shared": len(layout.shared_dp_group_ranks), "expert": len(layout.expert_dp_group_ranks)}
+    out["gradient all-reduce"] = sum(shard.parameters[g] * elem for g in shard.parameters if replicas[g] > 1)
+    micro_tokens = cfg.trainer.per_device_batch_size // rt.num_microbatches * m.max_seq_len
+    n_layers = shard.layers[1] - shard.layers[0]
+    if rt.ep_size > 1:
+        rows = micro_tokens * m.top_k
+        out["expert exchange"] = 4 * n_layers * rt.num_microbatches * rows * m.d_model * elem * (rt.ep_size - 1) // rt.ep_size
+    if rt.pp_size > 1:
+        sides = (0 if layout.is_pp_first_stage else 1) + (0 if layout.is_pp_last_stage else 1)
+        out["pipeline boundaries"] = sides * rt.num_microbatches * micro_tokens * m.d_model * elem
+    return out
+
+
 def measured_sustained_tflops(default: float = 1400.0) -> float:
     """`bf16_tflops_sustained` of MEASURED_PEAKS.json next to the package's parent folder, else `default`."""
     from pathlib import Path
@@ -179,7 +201,10 @@ def measured_sustained_tflops(default: float = 1400.0) -> float:
         return default
 
 
-def render(shards: list[ShardPlan], hbm_gb: float) -> str:
+LINK_GBS = 770.0  # measured peer-copy bandwidth per direction; 900 is the nominal figure
+
+
+def render(shards: list[ShardPlan], hbm_gb: float, cfg: AppConfig | None = None) -> str:
     lines = []
     for s in shards:
         lines.append(f"pipeline stage {s.pp_rank}, expert rank {s.ep_rank} (ranks {s.ranks}): layers {s.layers[0]}..{s.layers[1] - 1}, "
@@ -191,6 +216,13 @@ def render(shards: list[ShardPlan], hbm_gb: float) -> str:
         share = s.total / (hbm_gb * GB)
         verdict = "fits" if share < 0.9 else ("tight" if share < 1.0 else "DOES NOT FIT")
         lines.append(f"    {s.total / GB:10.2f} GB  total = {100 * share:.0f} % of {hbm_gb:.0f} GB: {verdict}")
+        if cfg is not None:
+            traffic = nvlink_bytes_per_step(cfg, s)
+            total = sum(traffic.values())
+            if total:
+                parts = ", ".join(f"{k} {v / GB:.3f} GB" for k, v in traffic.items() if v)
+                lines.append(f"    NVLink per step and direction: {parts}: >= {total / (LINK_GBS * 1e9) * 1e3:.2f} ms at "
+                             f"{LINK_GBS:.0f} GB/s if nothing overlapped")
     return "\n".join(lines)
 
 
@@ -207,9 +239,10 @@ def main(argv=None) -> int:
     shards = plan(cfg, args.capacity_factor)
     floor = step_floor(cfg, args.sustained_tflops or measured_sustained_tflops())
     if args.json:
-        print(json.dumps({"shards": [dict(asdict(s), total=s.total) for s in shards], "step": floor}, indent=1))
+        print(json.dumps({"shards": [dict(asdict(s), total=s.total, nvlink_bytes_per_step=nvlink_bytes_per_step(cfg, s)) for s in shards],
+                          "step": floor}, indent=1))
     else:
-        print(render(shards, args.hbm_gb))
+        print(render(shards, args.hbm_gb, cfg))
         print(f"one step: {floor['tokens_per_step']} tokens, {floor['tflop_per_step']:.2f} TFLOP of model math over {floor['gpus']} GPU(s): "
               f">= {floor['floor_ms']:.2f} ms at {args.sustained_tflops or measured_sustained_tflops():.0f} TFLOP/s per GPU")
     return 0 if all(s.total < args.hbm_gb * GB for s in shards) else 1

@@ -77,3 +77,19 @@ def test_command_line(tmp_path, capsys):
     rows = out["shards"]
     assert len(rows) == 2 and rows[0]["total"] == sum(rows[0]["bytes"].values())
     assert out["step"]["gpus"] == 2 and out["step"]["tokens_per_step"] == 2 * 2 * 8 and out["step"]["floor_ms"] > 0
+
+
+def test_nvlink_traffic_by_cause():
+    from nanotitan_b200 import plan
+
+    cfg = tiny_app_cfg(dp=2, pp=2, ep=2, microbatches=2, batch=4, dtype="bfloat16")  # d 16, seq 8, top-2, 2 layers
+    first, *_, last = plan.plan(cfg)
+    a, b = plan.nvlink_bytes_per_step(cfg, first), plan.nvlink_bytes_per_step(cfg, last)
+    # shared parameters are replicated over dp x ep = 4 ranks, experts over dp = 2: both groups all-reduce
+    assert a["gradient all-reduce"] == 2 * (first.parameters["shared"] + first.parameters["expert"])
+    # one layer per stage, two micro-batches of 2 x 8 tokens, top-2, half of the rows leave the GPU, four transfers
+    assert a["expert exchange"] == 4 * 1 * 2 * (2 * 8 * 2) * 16 * 2 // 2
+    # the first stage has one neighbour: activations out, gradients in - one direction each
+    assert a["pipeline boundaries"] == 1 * 2 * (2 * 8) * 16 * 2 == b["pipeline boundaries"]
+    alone = plan.plan(tiny_app_cfg(dtype="bfloat16"))[0]
+    assert sum(plan.nvlink_bytes_per_step(tiny_app_cfg(dtype="bfloat16"), alone).values()) == 0
