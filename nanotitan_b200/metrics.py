@@ -1,4 +1,5 @@
-"""Step metrics: typed values with a reduce op, one packed all-reduce, TensorBoard sink.
+"""Step metrics: typed values with a reduce op, one packed all-reduce, TensorBoard sink (plus the scalars
+as `metrics.jsonl` next to the event files).
 
 Metric names and the ScalarMetric / HistogramMetric contract follow the reference
 (src/metrics.py:10-42, src/train.py:32-56).  The reference issues one float64
@@ -37,19 +38,27 @@ class MetricsLogger:
 
         self.log_dir = Path(log_root) / run_name
         self.writer = SummaryWriter(log_dir=str(self.log_dir))
+        # the scalars again as one JSON object per line, for scripts (sweeps, regression checks) that do not
+        # want to parse TensorBoard event files
+        self._lines = (self.log_dir / "metrics.jsonl").open("a", encoding="utf-8")
 
     def log(self, step: int, metrics: dict[str, float | torch.Tensor]) -> None:
+        scalars = {"step": step}
         for name, value in metrics.items():
             if isinstance(value, torch.Tensor) and value.ndim > 0:
                 self.writer.add_histogram(name, value, step)
             else:
                 self.writer.add_scalar(name, float(value), step)
+                scalars[name] = float(value)
+        self._lines.write(json.dumps(scalars) + "\n")
+        self._lines.flush()
 
     def log_config(self, config_dict: dict) -> None:
         self.writer.add_text("config", json.dumps(config_dict, indent=2, default=str), 0)
 
     def close(self) -> None:
         self.writer.close()
+        self._lines.close()
 
 
 def reduce_metrics(

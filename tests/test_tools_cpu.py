@@ -50,6 +50,10 @@ def test_metrics_sink_writes_scalars_histograms_and_config(tmp_path):
     assert [e.value for e in events.Scalars("train/ce_loss")] == [4.0, 3.0, 2.0]
     assert len(events.Histograms("moe/layer_00/route_frac_dist")) == 3
     assert "config/text_summary" in events.Tags()["tensors"]
+    import json
+
+    lines = [json.loads(line) for line in (tmp_path / "run" / "metrics.jsonl").read_text().splitlines()]
+    assert lines == [{"step": i, "train/ce_loss": 4.0 - i} for i in range(3)]
 
 
 def _reduce_worker(rank, world):
