@@ -1,4 +1,4 @@
-"""Grid sweeps: ``python -m nanotitan_b200.sweep <sweep.toml> [--dry-run] [--log-level L]``.
+"""Grid sweeps: ``python -m nanotitan_b200.sweep <sweep.toml> [--dry-run] [--summarize] [--log-level L]``.
 
 A sweep file names a base config and lists values per dotted key
 (`"optim.lr" = [1e-3, 5e-4]`).  The runner works on the *flat* form of a config - a
@@ -118,14 +118,45 @@ def launch_command(config: dict[str, Any], config_path: Path, log_level: str) ->
             f"--nproc-per-node={ranks}", "-m", "nanotitan_b200.train", f"@{config_path}", f"--log.level={log_level}"]
 
 
+# ------------------------------------------------------------------ results
+def summarize(runs: list[tuple[str, dict[str, Any]]], log_root: Path = Path("runs"), tail: int = 10) -> list[dict[str, Any]]:
+    """One row per run from the `metrics.jsonl` its trainer wrote: steps logged, mean cross-entropy and mean
+    tokens/s over the last `tail` logged steps (None where a run has not logged anything yet)."""
+    rows = []
+    for name, _config in runs:
+        path = Path(log_root) / name / "metrics.jsonl"
+        records = []
+        if path.exists():
+            records = [json.loads(line) for line in path.read_text().splitlines() if line.strip()]
+            records = [r for r in records if "train/ce_loss" in r]
+        last = records[-tail:]
+
+        def mean(key):
+            values = [r[key] for r in last if key in r]
+            return sum(values) / len(values) if values else None
+
+        rows.append({"run": name, "steps": len(records), "ce_loss": mean("train/ce_loss"),
+                     "tokens_per_second": mean("train/tokens_per_second")})
+    return rows
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description="Run every point of a grid sweep described by a TOML file.")
+    parser.add_argument("--summarize", action="store_true",
+                        help="launch nothing: print what the runs of this sweep have logged so far, best loss first")
     parser.add_argument("sweep", type=Path, help="sweep TOML: base_config + [parameters]")
     parser.add_argument("--dry-run", action="store_true", help="validate and print the launch commands only")
     parser.add_argument("--log-level", default="INFO", help="logging level passed to the trainer")
     args = parser.parse_args(argv)
     base_path, runs = build_runs(args.sweep.resolve())
     print(f"{len(runs)} run(s) from {args.sweep} over {base_path}")
+    if args.summarize:
+        rows = sorted(summarize(runs), key=lambda r: (r["ce_loss"] is None, r["ce_loss"]))
+        for r in rows:
+            loss = "-" if r["ce_loss"] is None else f"{r['ce_loss']:.4f}"
+            rate = "-" if r["tokens_per_second"] is None else f"{r['tokens_per_second']:.0f}"
+            print(f"{loss:>10}  {rate:>12} tok/s  {r['steps']:>7} steps  {r['run']}")
+        return 0
     with tempfile.TemporaryDirectory(prefix="nt-sweep-") as scratch:
         for number, (name, config) in enumerate(runs, start=1):
             toml_path = Path(scratch) / f"{number:04d}-{name[:80]}.toml"

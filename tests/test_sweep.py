@@ -75,3 +75,22 @@ def test_reference_entry_path_is_importable():
     import scripts.sweep as entry
 
     assert entry.build_runs is sweep.build_runs and entry.main is sweep.main
+
+
+def test_summary_reads_what_the_runs_logged(tmp_path, monkeypatch, capsys):
+    import json
+
+    from nanotitan_b200 import sweep
+
+    monkeypatch.chdir(tmp_path)
+    runs = [("a", {}), ("b", {}), ("never-started", {})]
+    for name, losses in (("a", [5.0, 4.0, 3.0]), ("b", [5.0, 2.0])):
+        folder = tmp_path / "runs" / name
+        folder.mkdir(parents=True)
+        lines = [{"step": i, "train/ce_loss": v, "train/tokens_per_second": 100.0 * (i + 1)} for i, v in enumerate(losses)]
+        lines.append({"step": len(losses) - 1, "val/ce_loss": 9.0})  # validation records are not training steps
+        (folder / "metrics.jsonl").write_text("\n".join(json.dumps(x) for x in lines) + "\n")
+    rows = sweep.summarize(runs, tail=2)
+    assert rows[0] == {"run": "a", "steps": 3, "ce_loss": 3.5, "tokens_per_second": 250.0}
+    assert rows[1]["ce_loss"] == 3.5 and rows[1]["steps"] == 2
+    assert rows[2] == {"run": "never-started", "steps": 0, "ce_loss": None, "tokens_per_second": None}
