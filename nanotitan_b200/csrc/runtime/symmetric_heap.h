@@ -91,6 +91,12 @@ class FdChannel {
       : job_(job), rank_(rank), world_(world), timeout_ms_(timeout_ms) {
     sock_ = ::socket(AF_UNIX, SOCK_DGRAM | SOCK_CLOEXEC, 0);
     if (sock_ < 0) throw std::runtime_error(std::string("symmetric heap: socket(): ") + std::strerror(errno));
+    int on = 1;  // the kernel then attaches the sender's pid / uid / gid to every message we receive
+    if (::setsockopt(sock_, SOL_SOCKET, SO_PASSCRED, &on, sizeof(on)) != 0) {
+      int err = errno;
+      ::close(sock_);
+      throw std::runtime_error(std::string("symmetric heap: SO_PASSCRED: ") + std::strerror(err));
+    }
     sockaddr_un addr;
     socklen_t len = address_of(rank, &addr);
     if (::bind(sock_, reinterpret_cast<sockaddr*>(&addr), len) != 0) {
@@ -190,7 +196,7 @@ class FdChannel {
   void take_one() {
     Received r;
     iovec iov{&r.msg, sizeof(r.msg)};
-    alignas(cmsghdr) char control[CMSG_SPACE(sizeof(int))];
+    alignas(cmsghdr) char control[CMSG_SPACE(sizeof(int)) + CMSG_SPACE(sizeof(ucred))];
     msghdr hdr{};
     hdr.msg_iov = &iov;
     hdr.msg_iovlen = 1;
@@ -201,9 +207,17 @@ class FdChannel {
       if (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR) return;
       throw std::runtime_error(std::string("symmetric heap: recvmsg(): ") + std::strerror(errno));
     }
-    for (cmsghdr* c = CMSG_FIRSTHDR(&hdr); c != nullptr; c = CMSG_NXTHDR(&hdr, c))
-      if (c->cmsg_level == SOL_SOCKET && c->cmsg_type == SCM_RIGHTS) std::memcpy(&r.fd, CMSG_DATA(c), sizeof(int));
-    bool ok = n == static_cast<ssize_t>(sizeof(Message)) && r.msg.magic == Message().magic && r.msg.src >= 0 &&
+    bool same_user = false;  // the abstract socket name space is open to every local process: take our own user's only
+    for (cmsghdr* c = CMSG_FIRSTHDR(&hdr); c != nullptr; c = CMSG_NXTHDR(&hdr, c)) {
+      if (c->cmsg_level != SOL_SOCKET) continue;
+      if (c->cmsg_type == SCM_RIGHTS) std::memcpy(&r.fd, CMSG_DATA(c), sizeof(int));
+      if (c->cmsg_type == SCM_CREDENTIALS) {
+        ucred who;
+        std::memcpy(&who, CMSG_DATA(c), sizeof(who));
+        same_user = who.uid == ::geteuid();
+      }
+    }
+    bool ok = same_user && n == static_cast<ssize_t>(sizeof(Message)) && r.msg.magic == Message().magic && r.msg.src >= 0 &&
               r.msg.src < world_ && r.msg.src != rank_;
     if (!ok) {  // not one of ours: drop it, and the descriptor with it
       if (r.fd >= 0) ::close(r.fd);
