@@ -7,11 +7,13 @@ where `nanotitan_b200.ops.ext.get_ext()` looks for it.  Either route gives the s
 in-place build (`python -c 'import __graft_entry__ as g; g.build()'`) is incremental and needs no install.
 """
 import os
+import sys
 from pathlib import Path
 
 from setuptools import find_packages, setup
 
 ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))  # build front ends run this file from elsewhere; the source list lives in the package
 
 
 def extension():
