@@ -93,3 +93,23 @@ def test_nvlink_traffic_by_cause():
     assert a["pipeline boundaries"] == 1 * 2 * (2 * 8) * 16 * 2 == b["pipeline boundaries"]
     alone = plan.plan(tiny_app_cfg(dtype="bfloat16"))[0]
     assert sum(plan.nvlink_bytes_per_step(tiny_app_cfg(dtype="bfloat16"), alone).values()) == 0
+
+
+@pytest.mark.parametrize("name", ["dense_92m", "moe_ep8", "moe_3d", "dense_92m_cpu_ddp", "big_sabaka", "dist"])
+def test_shipped_configs_load_and_fit_one_gpu(name):
+    """Every configuration in configs/ validates against the schema, its layout tiles the ranks, and what it puts on
+    each GPU (worst-case expert capacity included) is below 180 GB."""
+    from pathlib import Path
+
+    from nanotitan_b200 import plan
+    from nanotitan_b200.config import load_config
+
+    cfg = load_config(Path(__file__).resolve().parent.parent / "configs" / f"{name}.toml")
+    shards = plan.plan(cfg)
+    world = cfg.runtime.dp_size * cfg.runtime.pp_size * cfg.runtime.ep_size
+    assert sorted(r for s in shards for r in s.ranks) == list(range(world))
+    assert sum(s.layers[1] - s.layers[0] for s in shards if s.ep_rank == 0) == cfg.model.n_layers
+    for s in shards:
+        assert s.total < 180e9, (name, s.pp_rank, s.ep_rank, s.total / 1e9)
+    floor = plan.step_floor(cfg, 1400.0)
+    assert floor["gpus"] == world and floor["floor_ms"] > 0
