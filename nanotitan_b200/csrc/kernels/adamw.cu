@@ -3,6 +3,8 @@
 // torch.optim.AdamW (decoupled weight decay, bias-corrected moments); `grad_scale` folds the
 // 1/N of a data-parallel mean in.  Optionally emits per-block sums of grad^2 for a gradient
 // norm, reduced in a fixed order by the caller.
+// The reference steps `torch.optim.AdamW(lr, weight_decay=0.1)` per parameter tensor (src/optim.py:6-10) with no
+// master weights.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <ATen/ATen.h>

@@ -1,4 +1,5 @@
-// Token cross-entropy over a padded logits matrix, forward and backward in one kernel.
+// Token cross-entropy over a padded logits matrix, forward and backward in one kernel (the reference calls
+// F.cross_entropy on fp32-cast logits and lets autograd build the backward, src/parallel/pp.py:76).
 //
 // One block per row.  Pass 1 streams the row once with an online (max, sum-exp) pair; pass 2
 // (the row is then in L2) overwrites the logits in place with

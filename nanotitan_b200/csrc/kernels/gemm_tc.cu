@@ -1,4 +1,7 @@
 // Host side of the tcgen05 GEMM: shape bookkeeping, TMA descriptors, tile-size choice, launch.
+// The dense, grouped-by-expert and weight-gradient products that the reference runs as nn.Linear / cuBLAS calls
+// (src/model/model.py:79-89, 128-182; src/model/feed_fwd.py:19-46) and as its SIMT kernels (csrc/kernels/gemm.cu:38-110,
+// grouped_gemm.cu:12-60, bwd_grouped_gemm_dX.cu, bwd_grouped_gemm_dW.cu) all come through `gemm_tc` here.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <ATen/ATen.h>

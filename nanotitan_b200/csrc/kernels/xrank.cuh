@@ -1,4 +1,5 @@
-// Cross-GPU flag barrier used inside kernels that exchange data over NVLink peer memory.
+// Cross-GPU flag barrier used inside kernels that exchange data over NVLink peer memory (the reference has no
+// device-side synchronisation between GPUs: every exchange is an NCCL call, src/model/moe_ops.py:139-145).
 // Every rank owns a pad of 32-bit words that all peers can write; "arriving" means storing the
 // current epoch (release, system scope) into one's own word of every peer's pad, "waiting" means
 // polling one's own pad (acquire, system scope) until every peer's word has reached the epoch.

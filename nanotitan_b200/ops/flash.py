@@ -1,4 +1,8 @@
-"""tcgen05 flash-attention kernels (forward and backward) behind an autograd Function."""
+"""tcgen05 flash-attention kernels (forward and backward) behind an autograd Function.
+
+The reference computes attention as softmax(QK^T / sqrt(Dh) + mask) V with a stored [1, 1, S, S] boolean mask
+(src/model/model.py:122-182); these kernels never form the S x S matrix.
+"""
 from __future__ import annotations
 
 import torch

@@ -11,7 +11,10 @@ the count matrix and a flag pad.  One layer's forward is
 and backward runs two pushes the other way round (combine-backward rows to the expert ranks,
 dispatch-backward rows home).  Compared with the NCCL path (`parallel/ep.py::_nccl_exchange`) there
 is no count collective, no split-size read-back, no packed copy on the home rank, no send / receive
-buffers and no regrouping gather / scatter; the host never waits inside a step.
+buffers and no regrouping gather / scatter; the host never waits inside a step.  The reference's
+expert-parallel path is its torch backend: a count all-to-all with a `.tolist()` read-back, two
+`all_to_all_single` per direction and a per-row Python loop that regroups the received rows
+(src/model/torch_backend.py:72-147, src/model/moe_ops.py:128-160).
 
 Memory.  X_in and Y of a layer stay alive until that layer's backward (they are what the weight
 gradient and the combine backward read), so they come from a pool of symmetric buffers: `acquire`

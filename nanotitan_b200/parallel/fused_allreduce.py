@@ -10,7 +10,9 @@ the owner's slice of the fp32 master weights and broadcasts the new bf16 paramet
 
 Symmetric memory comes from a provider in `parallel/symm_memory.py` (torch's, or this library's own heap)
 (plumbing); every byte that crosses NVLink is moved by `bucket_allreduce_kernel`.
-Set `NT_FUSED_ALLREDUCE=0` to keep the NCCL all-reduce (the measured baseline).
+Set `NT_FUSED_ALLREDUCE=0` to keep the NCCL all-reduce (the measured baseline).  The reference copies every
+gradient into a bucket, all-reduces it with NCCL, divides and copies back (src/parallel/reducer.py:103-145),
+then runs a separate optimizer pass.
 """
 from __future__ import annotations
 

@@ -4,6 +4,9 @@ Each rank rewrites `<dir>/rank_<r>.json` after every step (atomic rename).
 `stale_ranks` lists ranks whose file is missing or older than a limit.  Nothing here
 touches a GPU: a lost rank is found on the host before the next collective is
 launched, and the process-group timeout ends a collective that was already posted.
+
+The reference has no failure detection (its loop only destroys the process group in a `finally`,
+src/train.py:149, 224-226).
 """
 from __future__ import annotations
 
