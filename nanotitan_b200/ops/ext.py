@@ -89,3 +89,51 @@ def get_ext() -> ModuleType:
 def native(t) -> bool:
     """True when `t` lives on a GPU, where the CUDA kernels are the code path."""
     return t.is_cuda
+
+
+# ------------------------------------------------------------------ type stub
+STUB_PATH = Path(__file__).resolve().parent / f"{EXT_NAME}.pyi"
+
+
+def stub_text() -> str:
+    """A .pyi for the built extension, from the signatures pybind11 puts in the first docstring line."""
+    import re
+
+    ext = get_ext()
+
+    def clean(sig: str) -> str:
+        sig = sig.replace("torch.Tensor", "Tensor")
+        sig = re.sub(r"collections\.abc\.Sequence\[([^\]]+)\]", r"list[\1]", sig)
+        sig = sig.replace("typing.SupportsInt", "int").replace("typing.SupportsFloat", "float")
+        return re.sub(rf"self: {EXT_NAME}\.\w+", "self", sig)
+
+    out = [f'"""Type stub of the `{EXT_NAME}` extension, generated from the signatures pybind11 records',
+           "(`python -m nanotitan_b200.ops.ext --stub` rewrites it).  The module itself is built from nanotitan_b200/csrc",
+           'and loaded by `nanotitan_b200.ops.ext.get_ext()`."""',
+           "from __future__ import annotations", "", "import torch", "", "Tensor = torch.Tensor", ""]
+    for name in sorted(n for n in dir(ext) if not n.startswith("_")):
+        obj = getattr(ext, name)
+        doc = (obj.__doc__ or "").strip().splitlines()
+        if isinstance(obj, type):
+            out.append(f"class {name}:")
+            for member in sorted(m for m in dir(obj) if not m.startswith("_") or m == "__init__"):
+                first = (getattr(obj, member).__doc__ or "").strip().splitlines()[:1]
+                if first and first[0].startswith(member + "("):
+                    out.append(f"    def {clean(first[0])}: ...")
+                else:
+                    out.append(f"    {member}: int")
+            out.append("")
+        elif doc and doc[0].startswith(name + "("):
+            out.append(f"def {clean(doc[0])}:")
+            rest = " ".join(x.strip() for x in doc[1:] if x.strip())
+            out.append(f'    """{rest}"""' if rest else "    ...")
+            out.append("")
+    return "\n".join(out) + "\n"
+
+
+if __name__ == "__main__":
+    if "--stub" in sys.argv:
+        STUB_PATH.write_text(stub_text())
+        print(f"wrote {STUB_PATH}")
+    else:
+        print(build_extension(verbose="--verbose" in sys.argv))

@@ -136,3 +136,11 @@ def test_function_class_spellings_reach_the_same_operations():
     torch.testing.assert_close(y, x * gates.sum(1, keepdim=True), rtol=1e-5, atol=1e-6)
     with pytest.raises(TypeError):
         moe_ops.PackTokensFN()
+
+
+def test_type_stub_matches_the_built_extension():
+    from nanotitan_b200.ops import ext
+
+    if not ext.have_ext():
+        pytest.skip("the extension is not built")
+    assert ext.STUB_PATH.read_text() == ext.stub_text(), "run `python -m nanotitan_b200.ops.ext --stub`"
